@@ -72,7 +72,7 @@ __device__ __forceinline__ void split_pack_h2(const float a, const float b, uint
 }
 
 // ---------------------------------------------------------------------------------------
-// mbarrier + 1-D bulk TMA (cp.async.bulk -> SASS UBLKCP)
+// mbarrier + 1-D bulk TMA (cp.async.bulk)
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -227,7 +227,7 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
 
 // ---------------------------------------------------------------------------------------
 // tcgen05 (5th-gen tensor core) wrappers: TMEM allocation, single-thread MMA issue, commit to an
-// mbarrier, TMEM -> register loads.  SASS: UTCHMMA / UTCBAR / LDTM.
+// mbarrier, TMEM -> register loads.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -267,7 +267,7 @@ __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, 
         "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// 16 registers per thread -> 32 lanes x 16 consecutive 32-bit columns (lane i of the warp = TMEM lane base+i); SASS: STTM
+// 16 registers per thread -> 32 lanes x 16 consecutive 32-bit columns (lane i of the warp = TMEM lane base+i)
 __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
