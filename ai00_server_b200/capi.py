@@ -37,10 +37,12 @@ class Options(C.Structure):
     _fields_ = [("struct_bytes", C.c_uint32), ("max_batch", C.c_int32), ("token_chunk_size", C.c_int32), ("precision", C.c_int32),
                 ("num_devices", C.c_int32), ("devices", C.c_int32 * 8), ("num_lora", C.c_int32),
                 ("lora_st", C.c_void_p * MAX_LORA), ("lora_len", C.c_size_t * MAX_LORA), ("lora_alpha", C.c_float * MAX_LORA),
-                ("quant_layers", C.c_int32), ("quant_type", C.c_int32)]
+                ("quant_layers", C.c_int32), ("quant_type", C.c_int32),
+                ("config_json", C.c_void_p), ("config_len", C.c_size_t), ("kv_tokens", C.c_int32), ("kv_page", C.c_int32)]
 
 
 QUANT_NONE, QUANT_INT8, QUANT_NF4 = 0, 1, 2
+ARCH_KEMIRAX = 100          # Info.version of the config.json-described family
 
 
 class B200Error(RuntimeError):
@@ -69,6 +71,7 @@ SYMBOLS = [
     ("b200rwkv_state_read", C.c_int32, [_P, C.c_int32, C.POINTER(C.c_uint64)]),
     ("b200rwkv_state_write", C.c_int32, [_P, C.c_int32, C.c_uint64]),
     ("b200rwkv_state_free", C.c_int32, [_P, C.c_uint64]),
+    ("b200rwkv_state_reset", C.c_int32, [_P, C.c_int32]),
     ("b200rwkv_snapshot_back", C.c_int32, [_P, C.c_uint64, _P, _P]),
     ("b200rwkv_snapshot_load", C.c_int32, [_P, _P, _P, C.POINTER(C.c_uint64)]),
     ("b200rwkv_cache_stats", C.c_int32, [_P, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),

@@ -30,6 +30,11 @@
 #include "streamtest.cuh"
 #endif
 #include "wkv.cuh"
+#include "linear.cuh"
+#include "rmsnorm.cuh"
+#include "latent_attn.cuh"
+#include "gla.cuh"
+#include "moe.cuh"
 
 namespace b200 {
 
@@ -279,6 +284,14 @@ private:
 static b200rwkv_info derive_info(const StFile& st) {
     b200rwkv_info o;
     memset(&o, 0, sizeof(o));
+    if (st.find("embed") && st.find("l0.norm1") && st.find("final.norm")) {      // Kemirax family: sizes of its layers are in config.json
+        const StTensor& e = *st.find("embed");
+        o.version = B200RWKV_ARCH_KEMIRAX;
+        o.num_vocab = (int)StFile::dim(e, 0, "embed", 2);
+        o.num_emb = (int)StFile::dim(e, 1, "embed", 2);
+        while (st.find("l" + std::to_string(o.num_layer) + ".norm1")) ++o.num_layer;
+        return o;
+    }
     o.num_vocab = (int)st.dim("emb.weight", 0, 2);
     o.num_emb = (int)st.dim("emb.weight", 1, 2);
     int L = 0;
@@ -384,9 +397,11 @@ struct Profiler {
     std::vector<Rec> recs;
 };
 
-struct Snapshot { float* buf = nullptr; float* logits = nullptr; size_t bytes = 0; };   // CachedItem {state, output} on the device (run.rs:199-205)
+struct Snapshot { float* buf = nullptr; float* logits = nullptr; size_t bytes = 0; int pos = 0; };   // CachedItem {state, output} on the device (run.rs:199-205)
 
 }  // namespace b200
+
+#include "kemirax.cuh"
 
 using namespace b200;
 
@@ -488,6 +503,19 @@ struct b200rwkv_engine {
                      int top_k, uint32_t* ids_out, float* probs_out);
 
     std::mutex mu, sm_mu;
+
+    // Kemirax family (kemirax.cuh): set instead of `layers` when the model comes with a config.json of that architecture
+    std::unique_ptr<Kemirax> kx;
+    int kv_tokens = 0, kv_page = 0;               // attention cache capacity (tokens over all live sequences) and page size
+    void kx_build(const StFile& st, const char* cfg_json, size_t cfg_len);
+    void kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int rows, int groups, bool force_exact = false);
+    void kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool decode, int nsplit, Profiler* prof);
+    void kx_fill_step(int* hm, const std::vector<int>& slots, const std::vector<int>& counts, bool* decode, int* nsplit);
+    void kx_run_step(int T, int R, bool decode, int nsplit);
+    void kx_release(int slot);
+    void kx_reset(int slot);
+    void kx_xfer(int slot, float* rec, int ctx_rows, bool import, int n);
+    size_t api_state_floats() const { return kx ? kx->flat_floats(kx->state_ctx) : (size_t)L * (N + 2) * C; }
 
     // LoRA files blended into the projection weights while they are uploaded (borrowed during build only)
     struct LoraSrc { const StFile* st; float alpha; };
@@ -1628,9 +1656,13 @@ void b200rwkv_engine::infer(int nslot, const int32_t* slot, const int32_t* ntok,
         int R = 0;
         const int T = fill_meta(hm, s_slots, s_counts, s_toks, s_out, &R);
         last_T = T;
+        bool kx_decode = false;
+        int kx_split = 1;
+        if (kx) kx_fill_step(hm, s_slots, s_counts, &kx_decode, &kx_split);
         CK(cudaMemcpyAsync(d_meta, hm, meta_ints * 4, cudaMemcpyHostToDevice, stream));
         CK(cudaEventRecord(meta_ev[mb], stream));
-        run_step(mt_bucket(T), R > 0 ? mt_bucket(R) : 0);
+        if (kx) kx_run_step(T, R, kx_decode, kx_split);
+        else run_step(mt_bucket(T), R > 0 ? mt_bucket(R) : 0);
         if (hidden_keep) {       // hidden rows of every token of this call (b200rwkv_last_hidden), in entry order
             int t0 = 0;
             for (size_t j = 0; j < s_entry.size(); ++j) {
@@ -1779,6 +1811,8 @@ void b200rwkv_engine::state_xform(int slot, bool import, float* snap) {
     CK(cudaGetLastError());
 }
 
+#include "kemirax_engine.cuh"
+
 // =========================================================================================
 // in-process tensor-parallel group
 // =========================================================================================
@@ -1894,7 +1928,8 @@ struct LoraArg { const uint8_t* st; size_t len; float alpha; };
 
 static int32_t create_rank(const uint8_t* st, size_t len, int32_t device, int32_t max_batch, int32_t token_chunk_size,
                            int32_t precision, int32_t rank, int32_t world, const std::vector<LoraArg>& lora, b200rwkv_engine** out,
-                           int32_t quant_layers = 0, int32_t quant_type = 0) {
+                           int32_t quant_layers = 0, int32_t quant_type = 0, const char* config_json = nullptr, size_t config_len = 0,
+                           int32_t kv_tokens = 0, int32_t kv_page = 0) {
     API_BEGIN((b200rwkv_engine*)nullptr)
     REQUIRE(out, B200RWKV_ERR_INVALID, "null out");
     *out = nullptr;
@@ -1933,7 +1968,15 @@ static int32_t create_rank(const uint8_t* st, size_t len, int32_t device, int32_
     e->quant_type = quant_layers == 0 ? (int)QT_NONE : quant_type;
     if (const char* v = dbg_env("B200RWKV_GRAPH")) e->use_graph = atoi(v) != 0;
     if (const char* v = dbg_env("B200RWKV_PDL")) e->use_pdl = atoi(v) != 0;
-    e->build(f);
+    REQUIRE(kv_tokens >= 0 && kv_page >= 0 && kv_page <= 4096, B200RWKV_ERR_INVALID, "bad kv_tokens / kv_page");
+    e->kv_tokens = kv_tokens; e->kv_page = kv_page;
+    // model registry: a config.json selects the family by its `architecture`; without one the tensor names do (RWKV v5 / v6 / v7)
+    if (config_json && config_len > 0) {
+        e->kx_build(f, config_json, config_len);
+    } else {
+        REQUIRE(derive_info(f).version != B200RWKV_ARCH_KEMIRAX, B200RWKV_ERR_INVALID, "this model needs its config.json (b200rwkv_options.config_json)");
+        e->build(f);
+    }
     e->loras.clear();            // the LoRA images are only borrowed during the build
     *out = e.release();
     API_END
@@ -2054,6 +2097,7 @@ static int32_t rank_infer(b200rwkv_engine* e, int32_t nslot, const int32_t* slot
 int32_t b200rwkv_state_shape(b200rwkv_engine* e, int64_t shape[4]) {
     API_BEGIN(e)
     REQUIRE(e && shape, B200RWKV_ERR_INVALID, "null argument");
+    if (e->kx) { shape[0] = (int64_t)e->api_state_floats(); shape[1] = shape[2] = shape[3] = 1; return B200RWKV_OK; }
     shape[0] = e->C; shape[1] = e->N + 2; shape[2] = e->L; shape[3] = 1;
     API_END
 }
@@ -2061,7 +2105,7 @@ int32_t b200rwkv_state_shape(b200rwkv_engine* e, int64_t shape[4]) {
 int32_t b200rwkv_state_init(b200rwkv_engine* e, float* out) {
     API_BEGIN(e)
     REQUIRE(e && out, B200RWKV_ERR_INVALID, "null argument");
-    const size_t n = (size_t)e->L * (e->N + 2) * e->C;
+    const size_t n = e->api_state_floats();
     if (e->init_state.empty()) memset(out, 0, n * 4);
     else memcpy(out, e->init_state.data(), n * 4);
     API_END
@@ -2073,7 +2117,18 @@ static int32_t rank_state_load(b200rwkv_engine* e, int32_t slot, const float* in
     REQUIRE(slot >= 0 && slot < e->S, B200RWKV_ERR_STATE, "slot out of range");
     std::lock_guard<std::mutex> lk(e->mu);
     CK(cudaSetDevice(e->dev));
-    const size_t n = (size_t)e->L * (e->N + 2) * e->C;
+    const size_t n = e->api_state_floats();
+    if (e->kx) {
+        // record: [0] = tokens held, then per layer the shift row, the recurrent state or `state_ctx` cache rows
+        const int held = (int)in[0];
+        REQUIRE(in[0] >= 0.f && (float)held == in[0] && held <= e->kx->state_ctx, B200RWKV_ERR_INVALID, "state tensor: bad token count");
+        CK(cudaMemcpyAsync(e->d_api, in, n * 4, cudaMemcpyHostToDevice, e->stream));
+        e->kx_xfer(slot, e->d_api, e->kx->state_ctx, true, held);
+        CK(cudaStreamSynchronize(e->stream));
+        std::lock_guard<std::mutex> lk2(e->keep_mu);
+        e->keep_valid[slot] = 0;
+        return B200RWKV_OK;
+    }
     CK(cudaMemcpyAsync(e->d_api, in, n * 4, cudaMemcpyHostToDevice, e->stream));
     e->state_xform(slot, true);
     CK(cudaStreamSynchronize(e->stream));
@@ -2086,7 +2141,15 @@ static int32_t rank_state_back(b200rwkv_engine* e, int32_t slot, float* out) {
     REQUIRE(slot >= 0 && slot < e->S, B200RWKV_ERR_STATE, "slot out of range");
     std::lock_guard<std::mutex> lk(e->mu);
     CK(cudaSetDevice(e->dev));
-    const size_t n = (size_t)e->L * (e->N + 2) * e->C;
+    const size_t n = e->api_state_floats();
+    if (e->kx) {
+        CK(cudaMemsetAsync(e->d_api, 0, n * 4, e->stream));
+        e->kx_xfer(slot, e->d_api, e->kx->state_ctx, false, 0);
+        CK(cudaMemcpyAsync(out, e->d_api, n * 4, cudaMemcpyDeviceToHost, e->stream));
+        CK(cudaStreamSynchronize(e->stream));
+        out[0] = (float)e->kx->pos[slot];
+        return B200RWKV_OK;
+    }
     e->state_xform(slot, false);
     CK(cudaMemcpyAsync(out, e->d_api, n * 4, cudaMemcpyDeviceToHost, e->stream));
     CK(cudaStreamSynchronize(e->stream));
@@ -2108,10 +2171,11 @@ static void snapshot_copy(b200rwkv_engine* e, int slot, float* buf, bool to_snap
 }
 
 // allocate a snapshot record (+ a logits row when this rank keeps them)
-static Snapshot snapshot_alloc(b200rwkv_engine* e, bool with_logits) {
+static Snapshot snapshot_alloc(b200rwkv_engine* e, bool with_logits, int pos = 0) {
     Snapshot sn;
     const size_t rec = 2 * (size_t)e->C + (size_t)e->Hl * e->N * e->N;
-    sn.bytes = rec * e->L * 4;
+    sn.bytes = e->kx ? e->kx->flat_floats(pos) * 4 : rec * e->L * 4;      // Kemirax: a compact record with `pos` cache rows per layer
+    sn.pos = pos;
     CK(cudaMalloc(&sn.buf, sn.bytes));
     if (with_logits) {
         cudaError_t ce = cudaMalloc(&sn.logits, (size_t)e->V * 4);
@@ -2132,9 +2196,10 @@ static int32_t rank_state_read(b200rwkv_engine* e, int32_t slot, uint64_t* snaps
         std::lock_guard<std::mutex> lk2(e->keep_mu);
         has_row = e->d_keep && e->keep_valid[slot];
     }
-    Snapshot sn = snapshot_alloc(e, has_row);
+    Snapshot sn = snapshot_alloc(e, has_row, e->kx ? e->kx->pos[slot] : 0);
     try {
-        snapshot_copy(e, slot, sn.buf, true);
+        if (e->kx) e->kx_xfer(slot, sn.buf, sn.pos, false, 0);
+        else snapshot_copy(e, slot, sn.buf, true);
         // the slot's last logits row travels with the state (CachedItem.output, run.rs:199-205): a cache hit can be sampled
         // on the device without re-running the last token
         if (has_row) CK(cudaMemcpyAsync(sn.logits, e->d_keep + (size_t)slot * e->V, (size_t)e->V * 4, cudaMemcpyDeviceToDevice, e->stream));
@@ -2158,7 +2223,8 @@ static int32_t rank_state_write(b200rwkv_engine* e, int32_t slot, uint64_t snaps
     auto it = e->snaps.find(snapshot_id);
     REQUIRE(it != e->snaps.end(), B200RWKV_ERR_STATE, "unknown snapshot id");
     CK(cudaSetDevice(e->dev));
-    snapshot_copy(e, slot, it->second.buf, false);
+    if (e->kx) e->kx_xfer(slot, it->second.buf, it->second.pos, true, it->second.pos);
+    else snapshot_copy(e, slot, it->second.buf, false);
     if (e->d_keep && it->second.logits)
         CK(cudaMemcpyAsync(e->d_keep + (size_t)slot * e->V, it->second.logits, (size_t)e->V * 4, cudaMemcpyDeviceToDevice, e->stream));
     CK(cudaEventRecord(e->step_done, e->stream));
@@ -2191,7 +2257,17 @@ static int32_t rank_snapshot_back(b200rwkv_engine* e, uint64_t snapshot_id, floa
     auto it = e->snaps.find(snapshot_id);
     REQUIRE(it != e->snaps.end(), B200RWKV_ERR_STATE, "unknown snapshot id");
     CK(cudaSetDevice(e->dev));
-    if (state_out) {
+    if (state_out && e->kx) {
+        // compact record (pos cache rows per layer) -> the state tensor's layout (state_ctx rows per layer), on the host
+        const Snapshot& sn = it->second;
+        REQUIRE(sn.pos <= e->kx->state_ctx, B200RWKV_ERR_STATE, "snapshot is longer than the state tensor's cache rows");
+        std::vector<float> tmp(e->kx->flat_floats(sn.pos));
+        CK(cudaMemcpyAsync(tmp.data(), sn.buf, tmp.size() * 4, cudaMemcpyDeviceToHost, e->stream));
+        CK(cudaStreamSynchronize(e->stream));
+        memset(state_out, 0, e->api_state_floats() * 4);
+        kx_relayout(*e->kx, tmp.data(), sn.pos, state_out, e->kx->state_ctx, sn.pos);
+        state_out[0] = (float)sn.pos;
+    } else if (state_out) {
         const size_t n = (size_t)e->L * (e->N + 2) * e->C;
         e->state_xform(0, false, it->second.buf);
         CK(cudaMemcpyAsync(state_out, e->d_api, n * 4, cudaMemcpyDeviceToHost, e->stream));
@@ -2209,11 +2285,19 @@ static int32_t rank_snapshot_load(b200rwkv_engine* e, const float* state_in, con
     REQUIRE(e && state_in && snapshot_id, B200RWKV_ERR_INVALID, "null argument");
     std::lock_guard<std::mutex> lk(e->mu);
     CK(cudaSetDevice(e->dev));
-    Snapshot sn = snapshot_alloc(e, logits_in != nullptr && e->d_keep != nullptr);
+    const int held = e->kx ? (int)state_in[0] : 0;
+    REQUIRE(!e->kx || (state_in[0] >= 0.f && held <= e->kx->state_ctx), B200RWKV_ERR_INVALID, "state tensor: bad token count");
+    Snapshot sn = snapshot_alloc(e, logits_in != nullptr && e->d_keep != nullptr, held);
     try {
+        if (e->kx) {
+            std::vector<float> tmp(e->kx->flat_floats(held), 0.f);
+            kx_relayout(*e->kx, state_in, e->kx->state_ctx, tmp.data(), held, held);
+            CK(cudaMemcpy(sn.buf, tmp.data(), tmp.size() * 4, cudaMemcpyHostToDevice));
+        } else {
         const size_t n = (size_t)e->L * (e->N + 2) * e->C;
         CK(cudaMemcpyAsync(e->d_api, state_in, n * 4, cudaMemcpyHostToDevice, e->stream));
         e->state_xform(0, true, sn.buf);
+        }
         if (sn.logits) CK(cudaMemcpyAsync(sn.logits, logits_in, (size_t)e->V * 4, cudaMemcpyHostToDevice, e->stream));
         CK(cudaStreamSynchronize(e->stream));
     } catch (...) {
@@ -2648,6 +2732,20 @@ int32_t b200rwkv_debug_read(b200rwkv_engine* e, const char* name, float* out, si
         CK(cudaStreamSynchronize(e->stream));
         const std::string n(name);
         const int T = std::max(e->last_T, 1);
+        if (e->kx) {
+            // "layers_on": keep the residual stream after every layer of the following steps (un-graphed); "layers": read it,
+            // [num_layer][128 token rows][num_emb]
+            Kemirax& m = *e->kx;
+            if (n == "layers_on") {
+                if (!m.dbg_layers) m.dbg_layers = (float*)e->dalloc((size_t)e->L * e->maxT * m.W * 4);
+                e->use_graph = false;
+                return m.W;
+            }
+            REQUIRE(n == "layers" && m.dbg_layers, B200RWKV_ERR_INVALID, "unknown debug buffer: " + n);
+            REQUIRE((size_t)e->L * e->maxT * m.W <= cap, B200RWKV_ERR_INVALID, "debug buffer too small");
+            CK(cudaMemcpy(out, m.dbg_layers, (size_t)e->L * e->maxT * m.W * 4, cudaMemcpyDeviceToHost));
+            return m.W;
+        }
         struct F { const char* n; float* p; int cols; };
         const F fs[] = {{"x_a", e->x_a, e->C}, {"x_b", e->x_b, e->C}, {"xx1", e->xx1, e->C}, {"sx1", e->sx1, e->C}, {"xx2", e->xx2, e->C},
                         {"r", e->f_r, e->Cl}, {"k", e->f_k, e->Cl}, {"v", e->f_v, e->Cl}, {"g", e->f_g, e->Cl}, {"w", e->f_w, e->Cl},
@@ -2898,6 +2996,25 @@ int32_t b200rwkv_state_back(b200rwkv_engine* e, int32_t slot, float* out) {
     for (size_t r = 1; r < part.size(); ++r) merge_state_columns(e, out, part[r].data(), (int)r);
     return st;
 }
+static int32_t rank_state_reset(b200rwkv_engine* e, int32_t slot) {
+    API_BEGIN(e)
+    REQUIRE(e, B200RWKV_ERR_INVALID, "null engine");
+    REQUIRE(slot >= 0 && slot < e->S, B200RWKV_ERR_STATE, "slot out of range");
+    if (!e->kx) {
+        std::vector<float> init(e->api_state_floats(), 0.f);
+        if (!e->init_state.empty()) init = e->init_state;
+        return rank_state_load(e, slot, init.data());
+    }
+    std::lock_guard<std::mutex> lk(e->mu);
+    CK(cudaSetDevice(e->dev));
+    e->kx_reset(slot);
+    CK(cudaStreamSynchronize(e->stream));
+    std::lock_guard<std::mutex> lk2(e->keep_mu);
+    e->keep_valid[slot] = 0;
+    API_END
+}
+int32_t b200rwkv_state_reset(b200rwkv_engine* e, int32_t slot) { return RANKS(e, rank_state_reset(er, slot)); }
+
 int32_t b200rwkv_state_read(b200rwkv_engine* e, int32_t slot, uint64_t* snapshot_id) {
     if (!e || !e->group) return rank_state_read(e, slot, snapshot_id);
     // every rank snapshots its shard; the ranks' id counters advance in lockstep, so the ids agree
@@ -2985,6 +3102,13 @@ int32_t b200rwkv_profile_insitu(b200rwkv_engine* e, int32_t nslot, const int32_t
 int32_t b200rwkv_create_ex(const uint8_t* st, size_t len, const b200rwkv_options* opt, b200rwkv_engine** out) {
     if (!out || !opt) { g_err = "null argument"; return B200RWKV_ERR_INVALID; }
     *out = nullptr;
+    b200rwkv_options full;
+    memset(&full, 0, sizeof(full));
+    if (opt->struct_bytes == offsetof(b200rwkv_options, config_json)) {      // callers built against the header without the config fields
+        memcpy(&full, opt, opt->struct_bytes);
+        full.struct_bytes = sizeof(full);
+        opt = &full;
+    }
     if (opt->struct_bytes != sizeof(b200rwkv_options)) { g_err = "b200rwkv_options.struct_bytes does not match this library"; return B200RWKV_ERR_INVALID; }
     const int world = opt->num_devices <= 0 ? 1 : opt->num_devices;
     if (!(world == 1 || world == 2 || world == 4 || world == 8)) { g_err = "num_devices must be 1, 2, 4 or 8"; return B200RWKV_ERR_INVALID; }
@@ -2993,7 +3117,9 @@ int32_t b200rwkv_create_ex(const uint8_t* st, size_t len, const b200rwkv_options
     for (int i = 0; i < opt->num_lora; ++i) lora.push_back({opt->lora_st[i], opt->lora_len[i], opt->lora_alpha[i]});
     const int dev0 = opt->num_devices <= 0 ? 0 : opt->devices[0];
     if (world == 1)
-        return create_rank(st, len, dev0, opt->max_batch, opt->token_chunk_size, opt->precision, 0, 1, lora, out, opt->quant_layers, opt->quant_type);
+        return create_rank(st, len, dev0, opt->max_batch, opt->token_chunk_size, opt->precision, 0, 1, lora, out, opt->quant_layers, opt->quant_type,
+                           (const char*)opt->config_json, opt->config_len, opt->kv_tokens, opt->kv_page);
+    if (opt->config_json) { g_err = "models with a config.json run on one GPU in this version"; return B200RWKV_ERR_UNSUPPORTED; }
     if (opt->quant_layers > 0 && opt->quant_type != B200RWKV_QUANT_NONE) { g_err = "quantised layers are single-GPU in this version"; return B200RWKV_ERR_UNSUPPORTED; }
     for (int r = 0; r < world; ++r)
         for (int q = 0; q < r; ++q)

@@ -1,0 +1,140 @@
+// Routed mixture of experts around the grouped linear kernels (linear.cuh).
+//   moe_route_kernel     one warp per token: probabilities = softmax over all router outputs (real + identity experts, f32);
+//                        the `top` largest of (probability + selection bias) are chosen (ties: lower index), their weights
+//                        are the un-biased probabilities, not renormalised
+//   moe_group_kernel     one CTA: per-expert row counts, offsets and token lists in token order (deterministic), and for every
+//                        (token, choice) its compact row, or -1 for an identity expert
+//   moe_combine_kernel   x[t] += gate2[t] * ( sum_k w_k * (expert row | h[t] for an identity expert)
+//                                              + sigmoid(sg . h[t]) * shared[t] )                     (residual accumulate, f32)
+// The experts' matrices are stacked [E][...] so that one grouped launch covers all of them; rows are gathered by list.
+#pragma once
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int MOE_MAX_TOP = 8;
+
+struct MoeRouteParams {
+    const float* logits; int ld;              // [T, NE]
+    const float* bias;                        // [NE] selection bias (nullptr: none)
+    int NE, top;
+    int* sel;                                 // [T][top] expert index
+    float* wgt;                               // [T][top]
+    MetaView meta;
+};
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const MoeRouteParams p) {
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= p.meta.T()) return;
+    const float* z = p.logits + (size_t)t * p.ld;
+    float mx = -CUDART_INF_F;
+    for (int e = lane; e < p.NE; e += 32) mx = fmaxf(mx, z[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int e = lane; e < p.NE; e += 32) sum += expf(z[e] - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+    unsigned long long taken_lo = 0ull;       // lanes keep their own "already chosen" marks: expert e = lane + 32 * i -> bit i
+    for (int k = 0; k < p.top; ++k) {
+        float best = -CUDART_INF_F; int bi = 0x7fffffff;
+        for (int e = lane, i = 0; e < p.NE; e += 32, ++i) {
+            if ((taken_lo >> i) & 1ull) continue;
+            const float c = expf(z[e] - mx) * inv + (p.bias ? p.bias[e] : 0.f);
+            if (c > best || (c == best && e < bi)) { best = c; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if ((bi & 31) == lane) taken_lo |= 1ull << (bi >> 5);
+        if (lane == 0) {
+            p.sel[(size_t)t * p.top + k] = bi;
+            p.wgt[(size_t)t * p.top + k] = expf(z[bi] - mx) * inv;
+        }
+    }
+}
+
+struct MoeGroupParams {
+    const int* sel; int top, E;               // real experts are 0 .. E-1
+    int* cnt; int* off; int* list;            // [E], [E], [T * top]
+    int* row_of;                              // [T][top] compact row or -1
+    MetaView meta;
+};
+
+__global__ void __launch_bounds__(256) moe_group_kernel(const MoeGroupParams p) {
+    extern __shared__ int moe_s_cnt[];
+    int* s_cnt = moe_s_cnt;            // [E] counts, then [E] offsets
+    int* s_off = s_cnt + p.E;
+    const int T = p.meta.T(), n = T * p.top;
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+        int c = 0;
+        for (int i = 0; i < n; ++i) c += (p.sel[i] == e);
+        s_cnt[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < p.E; ++e) { s_off[e] = acc; acc += s_cnt[e]; }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+        p.cnt[e] = s_cnt[e];
+        p.off[e] = s_off[e];
+        int w = s_off[e];
+        for (int i = 0; i < n; ++i)
+            if (p.sel[i] == e) { p.list[w] = i / p.top; p.row_of[i] = w; ++w; }
+    }
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        if (p.sel[i] >= p.E) p.row_of[i] = -1;
+}
+
+struct MoeCombineParams {
+    float* x;                                 // [T, W] residual, accumulated in place
+    const float* h;                           // [T, W] the feed-forward's input
+    const float* gate;  int ldg;              // [T, W] residual gate of the feed-forward
+    const float* rows;                        // [T * top, W] expert outputs, compact rows
+    const int* row_of; const float* wgt; int top;
+    const float* shared;                      // [T, W] shared expert output (nullptr: none)
+    const __nv_bfloat16* sg;                  // [W] shared-expert gate vector
+    int W;
+    MetaView meta;
+};
+
+__global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombineParams p) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    if (t >= p.meta.T()) return;
+    const int W = p.W;
+    float sgate = 0.f;
+    if (p.shared) {
+        float d = 0.f;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) d = fmaf(__bfloat162float(p.sg[c]), p.h[(size_t)t * W + c], d);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = d;
+        __syncthreads();
+        d = 0.f;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) d += red[w];
+        sgate = 1.f / (1.f + expf(-d));
+    }
+    int rows[MOE_MAX_TOP]; float wg[MOE_MAX_TOP];
+#pragma unroll
+    for (int k = 0; k < MOE_MAX_TOP; ++k)
+        if (k < p.top) { rows[k] = p.row_of[(size_t)t * p.top + k]; wg[k] = p.wgt[(size_t)t * p.top + k]; }
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float f = 0.f;
+#pragma unroll
+        for (int k = 0; k < MOE_MAX_TOP; ++k)
+            if (k < p.top) f = fmaf(wg[k], rows[k] >= 0 ? p.rows[(size_t)rows[k] * W + c] : p.h[(size_t)t * W + c], f);
+        if (p.shared) f = fmaf(sgate, p.shared[(size_t)t * W + c], f);
+        p.x[(size_t)t * W + c] += p.gate[(size_t)t * p.ldg + c] * f;
+    }
+}
+
+}  // namespace b200

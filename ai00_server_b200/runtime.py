@@ -94,6 +94,10 @@ class State:
         s = self.shape()
         return int(s[0] * s[1] * s[2] * s[3])
 
+    def reset(self, batch: int) -> None:
+        """The slot holds an empty sequence again (its cache pages return to the pool)."""
+        capi.check(capi.lib().b200rwkv_state_reset(self._m._h, batch), self._m._h)
+
     def _np_shape(self):
         c, r, l, _ = self.shape()
         return (int(l), int(r), int(c))        # numpy C-order view of web-rwkv [C, N+2, L, 1]
@@ -226,11 +230,13 @@ class Model:
 
     def __init__(self, st: np.ndarray, max_batch: int = 8, token_chunk_size: int = 128, device: int = 0,
                  precision: int = 0, rank: int = 0, world: int = 1, exact: bool = False, devices=None, lora=None,
-                 quant: int = 0, quant_type: int | str = 0):
+                 quant: int = 0, quant_type: int | str = 0, config: bytes | str | None = None, kv_tokens: int = 0, kv_page: int = 0):
         """devices: list of CUDA ordinals -> ONE engine object owning all tensor-parallel ranks (b200rwkv_create_ex);
         lora: list of (st_bytes, alpha) blended at load (reference lib.rs:466-485);
         quant / quant_type: the reload request's fields (lib.rs:211-215): the first `quant` layers in "Int8" or "NF4";
-        rank / world: one process per GPU instead (b200rwkv_create_tp + tp.connect)."""
+        rank / world: one process per GPU instead (b200rwkv_create_tp + tp.connect);
+        config: text of the model's config.json for families that come with one (architecture "Kemirax"); kv_tokens / kv_page:
+        capacity (tokens over all live sequences) and page size of their attention cache."""
         if isinstance(quant_type, str):
             kinds = {"none": capi.QUANT_NONE, "int8": capi.QUANT_INT8, "nf4": capi.QUANT_NF4, "sf4": 3}
             if quant_type.lower() not in kinds:
@@ -242,7 +248,9 @@ class Model:
         st = np.ascontiguousarray(st, dtype=np.uint8)
         h = C.c_void_p()
         L = capi.lib()
-        if devices is not None or lora or quantised:
+        if isinstance(config, str):
+            config = config.encode()
+        if devices is not None or lora or quantised or config:
             if world != 1:
                 raise capi.B200Error(capi.ERR_INVALID, "devices / lora / quant go through b200rwkv_create_ex (in-process ranks)")
             opt = capi.Options()
@@ -259,6 +267,10 @@ class Model:
                 opt.lora_st[i], opt.lora_len[i], opt.lora_alpha[i] = img.ctypes.data, img.size, float(alpha)
             opt.num_lora = len(lora or [])
             opt.quant_layers, opt.quant_type = (int(quant), int(quant_type)) if quantised else (0, 0)
+            if config:
+                self._cfg_keep = np.frombuffer(config, np.uint8).copy()
+                opt.config_json, opt.config_len = self._cfg_keep.ctypes.data, self._cfg_keep.size
+                opt.kv_tokens, opt.kv_page = int(kv_tokens), int(kv_page)
             capi.check(L.b200rwkv_create_ex(capi.ptr(st), st.size, C.byref(opt), C.byref(h)))
             self._lora_keep = []
         else:

@@ -100,7 +100,17 @@ typedef struct {
      * projection matrices in a weight-only quantised format; everything else stays f16).  Single GPU, precision 0 only. */
     int32_t quant_layers;
     int32_t quant_type;               /* B200RWKV_QUANT_* */
+    /* Model families that are described by a config.json beside the weights (architecture "Kemirax": parallel blocks of latent
+     * attention / gated linear attention + routed experts, bf16 weights): the JSON text, borrowed during the call.  NULL: the
+     * family is recognised from the tensor names (RWKV v5 / v6 / v7).  Such models keep an attention cache in pages of
+     * `kv_page` tokens (0 = 64) drawn from a pool sized for `kv_tokens` tokens over all live sequences (0 = 4096 per slot);
+     * precision 0 = bf16 tensor-core products with f32 accumulation for multi-token steps, 1 = every product in plain f32. */
+    const uint8_t* config_json;
+    size_t config_len;
+    int32_t kv_tokens;
+    int32_t kv_page;
 } b200rwkv_options;
+#define B200RWKV_ARCH_KEMIRAX 100     /* b200rwkv_info.version of that family (num_head / head_size are per layer there: 0) */
 #define B200RWKV_QUANT_NONE 0
 #define B200RWKV_QUANT_INT8 1         /* blocks of 128 inputs: f16 (min, max) + 8-bit codes */
 #define B200RWKV_QUANT_NF4 2          /* blocks of 64 inputs: f16 absmax + 4-bit NormalFloat codes */
@@ -155,6 +165,11 @@ int32_t b200rwkv_state_back(b200rwkv_engine*, int32_t slot, float* out);        
 int32_t b200rwkv_state_read(b200rwkv_engine*, int32_t slot, uint64_t* snapshot_id);  /* State::read  (device copy) */
 int32_t b200rwkv_state_write(b200rwkv_engine*, int32_t slot, uint64_t snapshot_id);  /* State::write */
 int32_t b200rwkv_state_free(b200rwkv_engine*, uint64_t snapshot_id);                 /* drop TensorGpu */
+/* The slot holds an empty sequence again: State::load(State::init()) without the host round trip.  For models with an
+ * attention cache this is also what gives a finished request's pages back to the pool.  Their state tensor (state_shape =
+ * [n, 1, 1, 1]) is a flat record: [0] = tokens held, then per layer the token-shift row, the recurrent state, or the cache
+ * rows (min(pool, 8192) rows per caching layer, the first [0] of them valid); snapshots hold only the valid rows. */
+int32_t b200rwkv_state_reset(b200rwkv_engine*, int32_t slot);
 
 /* Device-resident state cache.  The reference's cache holds `CachedItem { state: TensorCpu, output:
  * TensorCpu }` (crates/ai00-core/src/run.rs:199-205): every check-out / check-in is a State::load / State::back PCIe copy of
