@@ -271,3 +271,112 @@ def algorithmic_bytes_per_step(s: Shape | str, batch: int) -> int:
     else:
         p_layer = 5 * C * C + 2 * C * F + C * C + 12 * C
     return 2 * (L * p_layer + V * C + 4 * C) + batch * (2 * L * (H * N * N + 2 * C) * 4 + 2 * C + 4 * V)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Kemirax family (config.json + bf16 safetensors): random weights for tests and bench.py
+# ----------------------------------------------------------------------------------------------------------------------
+def to_bf16_bits(a: np.ndarray) -> np.ndarray:
+    """float32 -> bfloat16 bit patterns (round to nearest even)."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)
+
+
+def pack_st_bf16(tensors: dict) -> np.ndarray:
+    """safetensors image with every float tensor stored as BF16 (integer tensors as I32)."""
+    head, blobs, off = {}, [], 0
+    for name, a in tensors.items():
+        a = np.asarray(a)
+        if a.dtype.kind in "iu":
+            raw, dt = np.ascontiguousarray(a, np.int32).tobytes(), "I32"
+        else:
+            raw, dt = to_bf16_bits(a).tobytes(), "BF16"
+        head[name] = {"dtype": dt, "shape": list(a.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    hj = json.dumps(head).encode()
+    hj += b" " * (-len(hj) % 8)
+    return np.frombuffer(struct.pack("<Q", len(hj)) + hj + b"".join(blobs), np.uint8).copy()
+
+
+def kemirax_layer(kind: str, *, heads=4, dim=16, vdim=16, rot_dim=8, kv_rank=24, q_rank=20, kv_from=None, scale=None, base=10000.0,
+                  scaling=None, tau=8.0, experts=4, identity=1, top=2, ff=24, limit=2.0, shared_ff=32, shared_limit=1.5, mlp=True) -> dict:
+    """One entry of config['layers'].  kind: 'latent_attention' | 'gla'."""
+    if kind == "latent_attention":
+        rot = {"base": base, "dims": rot_dim}
+        if scaling:
+            rot["scaling"] = dict(scaling)
+        mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "rot": rot,
+                 "scale": float(scale if scale is not None else (dim + rot_dim) ** -0.5)}
+        if kv_from is not None:
+            mixer["kv_from"] = int(kv_from)
+    else:
+        mixer = {"heads": heads, "dim": dim, "vdim": vdim, "tau": float(tau)}
+    layer = {"type": kind, "mixer": mixer, "mlp": None}
+    if mlp:
+        layer["mlp"] = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top}, "expert": {"ff": ff, "limit": limit}}
+        if shared_ff:
+            layer["mlp"]["shared"] = {"ff": shared_ff, "limit": shared_limit}
+    return layer
+
+
+def make_kemirax(layers: list, width: int = 64, vocab: int = 96, eps: float = 1e-5, seed: int = 0, gain: float = 1.0, a_rank: int = 8):
+    """(config.json bytes, safetensors image, dict of float32 arrays rounded to bf16) for a random model of the family."""
+    rng = np.random.default_rng(seed)
+    W = width
+    t = {}
+
+    def mat(n, k, g=1.0):
+        return (rng.standard_normal((n, k)) * (g * gain / np.sqrt(k))).astype(np.float32)
+
+    t["embed"] = rng.standard_normal((vocab, W)).astype(np.float32)
+    for i, l in enumerate(layers):
+        p, m = "l%d." % i, l["mixer"]
+        t[p + "norm1"] = np.float32(rng.uniform(0.8, 1.2))
+        t[p + "shift"] = rng.uniform(0.0, 1.0, W).astype(np.float32)
+        for r in ("rg1", "rg2") if l.get("mlp") else ("rg1",):
+            t[p + r] = mat(W, W)
+            t[p + r + ".b"] = rng.uniform(-0.5, 1.0, W).astype(np.float32)
+        H, dn, dv = m["heads"], m["dim"], m["vdim"]
+        if l["type"] == "latent_attention":
+            dr, rk, rq = m["rot_dim"], m["kv_rank"], m["q_rank"]
+            t[p + "mix.dq"] = mat(rq, W)
+            t[p + "mix.dq.norm"] = rng.uniform(0.5, 1.5, rq).astype(np.float32)
+            t[p + "mix.uq"] = mat(H * (dn + dr), rq, 2.0)
+            if "kv_from" not in m:
+                t[p + "mix.dkv"] = mat(rk + dr, W, 2.0)
+                t[p + "mix.dkv.norm"] = rng.uniform(0.5, 1.5, rk).astype(np.float32)
+            t[p + "mix.uk"] = mat(H * dn, rk, 2.0)
+            t[p + "mix.uv"] = mat(H * dv, rk)
+            t[p + "mix.o"] = mat(W, H * dv)
+        else:
+            t[p + "mix.q"] = mat(H * dn, W)
+            t[p + "mix.k"] = mat(H * dn, W)
+            t[p + "mix.v"] = mat(H * dv, W)
+            t[p + "mix.g"] = mat(H * dv, W)
+            t[p + "mix.o"] = mat(W, H * dv)
+            t[p + "mix.norm"] = rng.uniform(0.5, 1.5, dv).astype(np.float32)
+            t[p + "mix.a1"] = mat(a_rank, W)
+            t[p + "mix.a2"] = mat(H * dn, a_rank, 2.0)
+            t[p + "mix.a2.b"] = rng.uniform(1.0, 4.0, H * dn).astype(np.float32)
+        f = l.get("mlp")
+        if f:
+            E, I = f["router"]["experts"], f["router"].get("identity", 0)
+            t[p + "mlp.router"] = mat(E + I, W, 2.0)
+            t[p + "mlp.correction"] = rng.uniform(-0.05, 0.05, E + I).astype(np.float32)
+            for e in range(E):
+                q = p + "mlp.e%d." % e
+                t[q + "gate"] = mat(f["expert"]["ff"], W, 2.0)
+                t[q + "up"] = mat(f["expert"]["ff"], W, 2.0)
+                t[q + "down"] = mat(W, f["expert"]["ff"])
+            if f.get("shared"):
+                t[p + "mlp.shared.gate"] = mat(f["shared"]["ff"], W, 2.0)
+                t[p + "mlp.shared.up"] = mat(f["shared"]["ff"], W, 2.0)
+                t[p + "mlp.shared.down"] = mat(W, f["shared"]["ff"])
+                t[p + "mlp.shared.sg"] = mat(1, W)
+    t["final.norm"] = np.float32(rng.uniform(0.8, 1.2))
+    t["head"] = mat(vocab, W)
+    cfg = {"architecture": "Kemirax", "layers": layers, "norm": {"eps": eps}, "vocab": vocab, "width": W}
+    bits = {k: to_bf16_bits(np.asarray(v, np.float32).reshape(np.shape(v))) for k, v in t.items()}
+    rounded = {k: (b.astype(np.uint32) << 16).view(np.float32).reshape(np.shape(t[k])).astype(np.float64) for k, b in bits.items()}
+    return json.dumps(cfg).encode(), pack_st_bf16(t), rounded
