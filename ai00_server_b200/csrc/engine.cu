@@ -2387,7 +2387,7 @@ void b200rwkv_host_free(void* p) {
 }
 
 static void build_decode_metas(b200rwkv_engine* e, int nslot, const int32_t* slot, const uint32_t* tokens, int nsteps,
-                               std::vector<int>& all) {
+                               std::vector<int>& all, std::vector<int>* splits = nullptr) {
     all.assign((size_t)nsteps * e->meta_ints, 0);
     std::vector<int> s_slots(slot, slot + nslot), s_counts(nslot, 1), s_out(nslot, 1);
     std::vector<const uint32_t*> s_toks(nslot);
@@ -2397,6 +2397,12 @@ static void build_decode_metas(b200rwkv_engine* e, int nslot, const int32_t* slo
         for (int i = 0; i < nslot; ++i) s_toks[i] = tokens + (size_t)st * nslot + i;
         int R = 0;
         e->fill_meta(all.data() + (size_t)st * e->meta_ints, s_slots, s_counts, s_toks, s_out, &R);
+        if (e->kx) {        // positions, cache pages and the context split of this step (the sequences grow by one token per step)
+            bool dec = true;
+            int ns = 1;
+            e->kx_fill_step(all.data() + (size_t)st * e->meta_ints, s_slots, s_counts, &dec, &ns);
+            if (splits) splits->push_back(ns);
+        }
     }
 }
 
@@ -2409,8 +2415,8 @@ static int32_t rank_bench_decode(b200rwkv_engine* e, int32_t nslot, const int32_
     std::lock_guard<std::mutex> lk(e->mu);
     CK(cudaSetDevice(e->dev));
     const int nsteps = warmup + steps;
-    std::vector<int> all;
-    build_decode_metas(e, nslot, slot, tokens, nsteps, all);
+    std::vector<int> all, splits;
+    build_decode_metas(e, nslot, slot, tokens, nsteps, all, &splits);
     long long launches_before = 0;
     int* d_all = nullptr;
     CK(cudaMalloc(&d_all, all.size() * 4));
@@ -2435,7 +2441,8 @@ static int32_t rank_bench_decode(b200rwkv_engine* e, int32_t nslot, const int32_
         }
         if (flush) CK(cudaMemsetAsync(flush, st & 0xff, flush_bytes, e->stream));
         CK(cudaMemcpyAsync(e->d_meta, d_all + (size_t)st * e->meta_ints, e->meta_ints * 4, cudaMemcpyDeviceToDevice, e->stream));
-        e->run_step(MT, MT);
+        if (e->kx) e->kx_run_step(nslot, nslot, true, splits[st]);
+        else e->run_step(MT, MT);
         if (step_ms_out && st >= warmup) CK(cudaEventRecord(marks[st - warmup], e->stream));
     }
     CK(cudaEventRecord(eb, e->stream));
@@ -2460,13 +2467,14 @@ static int32_t rank_profile_step(b200rwkv_engine* e, int32_t nslot, const int32_
     REQUIRE(nslot >= 1 && nslot <= e->S && nslot <= e->maxT, B200RWKV_ERR_INVALID, "bad argument");
     std::lock_guard<std::mutex> lk(e->mu);
     CK(cudaSetDevice(e->dev));
-    std::vector<int> all;
-    build_decode_metas(e, nslot, slot, tokens, 1, all);
+    std::vector<int> all, splits;
+    build_decode_metas(e, nslot, slot, tokens, 1, all, &splits);
     CK(cudaMemcpyAsync(e->d_meta, all.data(), e->meta_ints * 4, cudaMemcpyHostToDevice, e->stream));
     CK(cudaStreamSynchronize(e->stream));
     Profiler prof;
     const int MT = mt_bucket(nslot);
-    e->enqueue_step(e->stream, MT, MT, &prof);
+    if (e->kx) e->kx_enqueue_step(e->stream, kx_bucket(nslot), kx_bucket(nslot), true, splits[0], &prof);
+    else e->enqueue_step(e->stream, MT, MT, &prof);
     CK(cudaStreamSynchronize(e->stream));
     for (int i = 0; i < 4; ++i) { ms[i] = 0.f; launches[i] = 0; }
     for (auto& r : prof.recs) {

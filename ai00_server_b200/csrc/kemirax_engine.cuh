@@ -251,6 +251,10 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
         CK(cudaFuncSetAttribute(latent_attn_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         CK(cudaFuncSetAttribute(latent_attn_kernel<1, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         CK(cudaFuncSetAttribute(latent_attn_kernel<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        const int smem_tc = (int)latent_attn_tc_smem(m.max_D);
+        CK(cudaFuncSetAttribute(latent_attn_tc_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tc));
+        CK(cudaFuncSetAttribute(latent_attn_tc_kernel<1, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tc));
+        CK(cudaFuncSetAttribute(latent_attn_tc_kernel<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tc));
     }
     CK(cudaFuncSetAttribute(gla_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     CK(cudaDeviceSynchronize());
@@ -259,9 +263,12 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
 // one grouped linear launch; `rows` bounds the row count of any group (the step's bucket)
 void b200rwkv_engine::kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int rows, int groups, bool force_exact) {
     p.max_rows = rows;
-    if (rows <= LIN_SK_ROWS) {
+    const bool exact = kx->exact || force_exact;
+    if (!exact && rows <= 16) {
+        launch_k(lin_mma16_kernel, dim3(cdiv(p.N, 8), 1, groups), dim3(LIN_M16_WARPS * 32), 0, p, KC_GEMM, s, prof);
+    } else if (rows <= LIN_SK_ROWS || (exact && rows <= 16)) {
         launch_k(lin_skinny_kernel, dim3(cdiv(p.N, 2 * LIN_SK_WARPS), 1, groups), dim3(LIN_SK_WARPS * 32), 0, p, KC_GEMM, s, prof);
-    } else if (kx->exact || force_exact) {
+    } else if (exact) {
         launch_k(lin_tile_kernel<true>, dim3(cdiv(p.N, LIN_BN), cdiv(rows, LIN_BM), groups), dim3(LIN_THREADS), 0, p, KC_GEMM, s, prof);
     } else {
         launch_k(lin_tile_kernel<false>, dim3(cdiv(p.N, LIN_BN), cdiv(rows, LIN_BM), groups), dim3(LIN_THREADS), 0, p, KC_GEMM, s, prof);
@@ -316,7 +323,12 @@ void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool 
                 launch_k(kv_write_kernel, dim3(rows), dim3(128), 0, kw, KC_OTHER, s, prof);
             }
             LatentAttnParams ap{m.qa, l.cache, m.d_table, m.npages, m.page, m.part, H_, rk, dr, nsplit, c.scale, mv, m.sm};
-            if (!decode) {
+            if (!m.exact) {         // serving precision: both products on the tensor cores (TF32 operands, f32 accumulation and softmax)
+                const size_t sm_b = latent_attn_tc_smem(D);
+                if (!decode) launch_k(latent_attn_tc_kernel<4, 4>, dim3(cdiv(rows, 4) + nslot_grid, cdiv(H_, 4), nsplit), dim3(LA_THREADS), sm_b, ap, KC_WKV, s, prof);
+                else if (H_ > 8) launch_k(latent_attn_tc_kernel<1, 16>, dim3(rows, cdiv(H_, 16), nsplit), dim3(LA_THREADS), sm_b, ap, KC_WKV, s, prof);
+                else launch_k(latent_attn_tc_kernel<2, 8>, dim3(rows, cdiv(H_, 8), nsplit), dim3(LA_THREADS), sm_b, ap, KC_WKV, s, prof);
+            } else if (!decode) {
                 launch_k(latent_attn_kernel<4, 4>, dim3(cdiv(rows, 4) + nslot_grid, cdiv(H_, 4), nsplit), dim3(LA_THREADS), latent_attn_smem<4, 4>(D), ap,
                          KC_WKV, s, prof);
             } else if (H_ > 8) {

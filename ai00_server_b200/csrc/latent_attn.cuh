@@ -249,6 +249,185 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attn_kernel(const LatentAtt
     }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Tensor-core variant for the serving precision: the same CTA shape (16 (token, head) rows, 32-key tiles, online softmax in
+// f32) with both products on mma.sync m16n8k8 TF32 (operands rounded to TF32 with cvt.rna, f32 accumulation):
+//   scores  S[16 x 32]  = Q[16 x D] . K^T      warp w owns keys 8w .. 8w+7, D / 8 k-steps
+//   output  O[16 x rk] += P[16 x 32] . C       warp w owns a quarter of the latent channels, 4 k-steps per 8 channels
+// Scores go through shared memory between the two so that the softmax keeps the row-per-warp form of the f32 kernel.
+// Row strides are = 4 (mod 32) floats: fragment loads of the score phase are bank-conflict free.
+// ------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t to_tf32(float v) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32_1688(float c[4], const uint32_t a[4], const uint32_t b[2]) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__host__ __device__ inline int la_pad8(int n) { return (n + 7) & ~7; }
+__host__ __device__ inline int la_stride(int D) { const int dp = la_pad8(D); return dp + ((4 - dp % 32) + 32) % 32; }
+__host__ __device__ inline size_t latent_attn_tc_smem(int D) {
+    return ((size_t)16 * la_stride(D) + (size_t)LA_KT * la_stride(D) + 16 * 36 + 64) * sizeof(float);
+}
+constexpr int LA_TC_MAX_NT = 16;                   // 8-channel tiles per warp: rk <= 512
+
+template <int QB, int HG>
+__global__ void __launch_bounds__(LA_THREADS) latent_attn_tc_kernel(const LatentAttnParams p) {
+    static_assert(QB * HG == 16, "one m16 tile of (token, head) rows");
+    const int ci = blockIdx.x;
+    if (ci >= p.sm.n_chunks()) return;
+    const int t0 = p.sm.chunk_start()[ci], nt = p.sm.chunk_count()[ci];
+    const int h0 = blockIdx.y * HG;
+    const int D = p.rk + p.dr, rk = p.rk, Dp = la_pad8(D), DS = la_stride(D);
+    const int slot = p.meta.tok_slot()[t0];
+    const int pos0 = p.sm.tok_pos()[t0];
+    const int nkeys = pos0 + nt;
+    const int tiles = (nkeys + LA_KT - 1) / LA_KT;
+    const int per = (tiles + p.nsplit - 1) / p.nsplit;
+    const int tile_lo = blockIdx.z * per, tile_hi = min(tiles, tile_lo + per);
+
+    extern __shared__ __align__(16) float la_tc_smem[];
+    float* sq = la_tc_smem;                        // [16][DS]
+    float* sk = sq + (size_t)16 * DS;              // [LA_KT][DS]
+    float* ss = sk + (size_t)LA_KT * DS;           // [16][36] scores, then probabilities
+    float* scorr = ss + 16 * 36;                   // [16] rescale of the running output
+    float* sml = scorr + 16;                       // [16][2] final (m, l)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+
+    for (int e = threadIdx.x; e < 16 * DS; e += LA_THREADS) {
+        const int r = e / DS, d = e % DS;
+        const int qi = r / HG, h = h0 + r % HG;
+        sq[e] = (d < D && qi < nt && h < p.H) ? p.q[(size_t)(t0 + qi) * p.H * D + (size_t)h * D + d] : 0.f;
+    }
+    for (int e = threadIdx.x; e < LA_KT * (DS - D); e += LA_THREADS) {       // pad columns of the key tile stay zero
+        const int j = e / (DS - D), d = D + e % (DS - D);
+        sk[(size_t)j * DS + d] = 0.f;
+    }
+    constexpr int RPW = 4;
+    float m[RPW], l[RPW];
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) { m[i] = -CUDART_INF_F; l[i] = 0.f; }
+    const int cw = la_pad8((rk + 3) / 4);          // latent channels per warp, a multiple of 8
+    float o[LA_TC_MAX_NT][4];
+#pragma unroll
+    for (int n = 0; n < LA_TC_MAX_NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    const int* tab = p.table + (size_t)slot * p.stride;
+    const bool vec = (D % 4 == 0);
+    for (int tile = tile_lo; tile < tile_hi; ++tile) {
+        const int kb = tile * LA_KT;
+        __syncthreads();                           // the previous tile is consumed; sq and the pad columns are written
+        if (vec) {
+            const int cpr = D / 4;                 // 16-byte chunks per row
+            for (int e = threadIdx.x; e < LA_KT * cpr; e += LA_THREADS) {
+                const int j = e / cpr, c = e % cpr;
+                const int kj = kb + j;
+                float* dst = sk + (size_t)j * DS + c * 4;
+                if (kj < nkeys) {
+                    const float* src = p.cache + ((size_t)tab[kj / p.page] * p.page + kj % p.page) * D + c * 4;
+                    const uint32_t da = (uint32_t)__cvta_generic_to_shared(dst);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(da), "l"(src) : "memory");
+                } else {
+                    *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+        } else {
+            for (int e = threadIdx.x; e < LA_KT * D; e += LA_THREADS) {
+                const int j = e / D, d = e % D;
+                const int kj = kb + j;
+                sk[(size_t)j * DS + d] = kj < nkeys ? p.cache[((size_t)tab[kj / p.page] * p.page + kj % p.page) * D + d] : 0.f;
+            }
+        }
+        __syncthreads();
+        {   // scores of keys 8 * warp .. + 7
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const float* qa0 = sq + (size_t)gq * DS + tq;
+            const float* qa1 = sq + (size_t)(gq + 8) * DS + tq;
+            const float* kb0 = sk + (size_t)(warp * 8 + gq) * DS + tq;
+#pragma unroll 4
+            for (int ks = 0; ks < Dp; ks += 8) {
+                uint32_t a[4], b[2];
+                a[0] = to_tf32(qa0[ks]); a[1] = to_tf32(qa1[ks]); a[2] = to_tf32(qa0[ks + 4]); a[3] = to_tf32(qa1[ks + 4]);
+                b[0] = to_tf32(kb0[ks]); b[1] = to_tf32(kb0[ks + 4]);
+                mma_tf32_1688(acc, a, b);
+            }
+            ss[gq * 36 + warp * 8 + tq * 2] = acc[0]; ss[gq * 36 + warp * 8 + tq * 2 + 1] = acc[1];
+            ss[(gq + 8) * 36 + warp * 8 + tq * 2] = acc[2]; ss[(gq + 8) * 36 + warp * 8 + tq * 2 + 1] = acc[3];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) {            // softmax rows 4 * warp .. + 3, lane = key
+            const int r = warp * RPW + i;
+            const int qi = r / HG;
+            const bool live = qi < nt && (kb + lane) <= pos0 + qi;
+            const float sc = live ? ss[r * 36 + lane] * p.scale : -CUDART_INF_F;
+            float mx = sc;
+#pragma unroll
+            for (int of = 16; of > 0; of >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, of));
+            const float mn = fmaxf(m[i], mx);
+            float pj = 0.f, corr = 1.f;
+            if (mn > -CUDART_INF_F) {
+                pj = live ? expf(sc - mn) : 0.f;
+                corr = expf(m[i] - mn);
+            }
+            float ps = pj;
+#pragma unroll
+            for (int of = 16; of > 0; of >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, of);
+            l[i] = l[i] * corr + ps;
+            m[i] = mn;
+            ss[r * 36 + lane] = pj;
+            if (lane == 0) scorr[r] = corr;
+        }
+        __syncthreads();
+        {   // output: this warp's latent channels
+            uint32_t a[4][4];
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                a[ks][0] = to_tf32(ss[gq * 36 + ks * 8 + tq]); a[ks][1] = to_tf32(ss[(gq + 8) * 36 + ks * 8 + tq]);
+                a[ks][2] = to_tf32(ss[gq * 36 + ks * 8 + tq + 4]); a[ks][3] = to_tf32(ss[(gq + 8) * 36 + ks * 8 + tq + 4]);
+            }
+            const float c0 = scorr[gq], c1 = scorr[gq + 8];
+#pragma unroll
+            for (int n = 0; n < LA_TC_MAX_NT; ++n) {
+                const int cb = warp * cw + n * 8;
+                if (n * 8 >= cw || cb >= rk) break;
+                o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    uint32_t b[2];
+                    b[0] = to_tf32(sk[(size_t)(ks * 8 + tq) * DS + cb + gq]);
+                    b[1] = to_tf32(sk[(size_t)(ks * 8 + tq + 4) * DS + cb + gq]);
+                    mma_tf32_1688(o[n], a[ks], b);
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RPW; ++i)
+        if (lane == 0) { sml[(warp * RPW + i) * 2] = m[i]; sml[(warp * RPW + i) * 2 + 1] = l[i]; }
+    __syncthreads();
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+        const int r = gq + hrow * 8;
+        const int qi = r / HG, h = h0 + r % HG;
+        if (qi >= nt || h >= p.H) continue;
+        float* dst = p.part + (((size_t)(t0 + qi) * p.H + h) * p.nsplit + blockIdx.z) * (rk + 2);
+#pragma unroll
+        for (int n = 0; n < LA_TC_MAX_NT; ++n) {
+            const int cb = warp * cw + n * 8;
+            if (n * 8 >= cw || cb >= rk) break;
+            const int d = cb + tq * 2;
+            if (d < rk) dst[d] = o[n][hrow * 2];
+            if (d + 1 < rk) dst[d + 1] = o[n][hrow * 2 + 1];
+        }
+        if (warp == 0 && tq == 0) { dst[rk] = sml[r * 2]; dst[rk + 1] = sml[r * 2 + 1]; }
+    }
+}
+
 struct LatentMergeParams {
     const float* part;
     float* out;                                    // [T, H * rk]

@@ -5,10 +5,14 @@
 // memory (the step metadata, the router's per-expert counts), so a captured step graph never changes.
 //
 //   lin_tile_kernel<EXACT>   steps of many rows.  EXACT = false: bf16 operands on the tensor cores (mma.sync m16n8k16, f32
-//                            accumulate), activations rounded to bf16 while they are staged; EXACT = true: plain f32 FMA on
-//                            the f32 activations (bf16 weights widen exactly), no reduced-precision product anywhere.
-//   lin_skinny_kernel        decode-shaped steps (a few rows): one warp per output (pair), the weight row streamed once as
-//                            16-byte loads, f32 FMA for either precision -- the launch is bound by the weight bytes.
+//                            accumulate) behind a two-stage cp.async pipeline, activations rounded to bf16 when the fragments
+//                            are built; EXACT = true: plain f32 FMA on the f32 activations (bf16 weights widen exactly), no
+//                            reduced-precision product anywhere.
+//   lin_mma16_kernel         serving precision, steps of up to 16 rows (decode): the same tensor-core product with the k range
+//                            split over the warps of a CTA and every operand streamed straight from global memory; the launch
+//                            is bound by the weight bytes.
+//   lin_skinny_kernel        exact precision, a few rows: one warp per output pair, weight rows streamed as 16-byte loads, f32
+//                            FMA.
 //
 // Epilogues (fused): bias, sigmoid / silu, a per-row scale, accumulate-into-residual through a gate, and the clamped gated
 // unit of the experts on interleaved (gate, up) output pairs.
@@ -81,6 +85,15 @@ __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float2 v) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v.x, v.y);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 template <bool EXACT>
 __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p) {
     const int g = blockIdx.z;
@@ -143,9 +156,12 @@ __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p
             }
         }
     } else {
-        constexpr int LDS = LIN_BK + 8;                // 80-byte rows: fragment loads fall into distinct banks
-        __shared__ __align__(16) __nv_bfloat16 sA[LIN_BM][LDS];
-        __shared__ __align__(16) __nv_bfloat16 sB[LIN_BN][LDS];
+        // two-stage cp.async pipeline: slab i+1 streams into the other buffer while slab i is multiplied.  Activations are
+        // staged as f32 and rounded to bf16 when the fragments are built; weights are staged as stored.
+        constexpr int LDA = LIN_BK + 4;                // floats: 144-byte rows (16-byte aligned chunks, spread banks)
+        constexpr int LDB = LIN_BK + 8;                // bf16: 80-byte rows
+        __shared__ __align__(16) float sA[2][LIN_BM][LDA];
+        __shared__ __align__(16) __nv_bfloat16 sB[2][LIN_BN][LDB];
         const int warp = tid >> 5, lane = tid & 31;
         const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;      // 2 x 2 warps, 32 x 32 each
         const int gq = lane >> 2, tq = lane & 3;
@@ -159,44 +175,48 @@ __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p
         const bool vecW = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
         const bool vecX = (p.ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(X) & 15) == 0);
         __syncthreads();
-        for (int k0 = 0; k0 < K; k0 += LIN_BK) {
-            // activations: 64 rows x 32 k, 4 consecutive k per thread and pass
+        auto stage = [&](int buf, int k0) {
             for (int e = tid; e < LIN_BM * (LIN_BK / 4); e += LIN_THREADS) {
                 const int r = e / (LIN_BK / 4), k = (e % (LIN_BK / 4)) * 4;
                 const int xr = s_xrow[r];
-                float v[4] = {0.f, 0.f, 0.f, 0.f};
-                if (xr >= 0) {
-                    const float* src = X + (size_t)xr * p.ldx + k0 + k;
-                    if (vecX && k0 + k + 3 < K) {
-                        const float4 q = *reinterpret_cast<const float4*>(src);
-                        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
-                    } else {
+                float* dst = &sA[buf][r][k];
+                if (xr >= 0 && vecX && k0 + k + 3 < K) {
+                    cp_async16(dst, X + (size_t)xr * p.ldx + k0 + k);
+                } else {
+                    float v[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (xr >= 0) {
+                        const float* src = X + (size_t)xr * p.ldx + k0 + k;
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
                             if (k0 + k + j < K) v[j] = src[j];
                     }
+                    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
                 }
-                __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
-                *reinterpret_cast<__nv_bfloat162*>(&sA[r][k]) = lo;
-                *reinterpret_cast<__nv_bfloat162*>(&sA[r][k + 2]) = hi;
             }
-            // weights: 64 outputs x 32 k, 8 consecutive k per thread and pass
             for (int e = tid; e < LIN_BN * (LIN_BK / 8); e += LIN_THREADS) {
                 const int r = e / (LIN_BK / 8), k = (e % (LIN_BK / 8)) * 8;
                 const int n = n0 + r;
-                uint4 q = make_uint4(0, 0, 0, 0);
-                if (n < N) {
-                    const __nv_bfloat16* src = W + (size_t)n * K + k0 + k;
-                    if (vecW && k0 + k + 7 < K) {
-                        q = *reinterpret_cast<const uint4*>(src);
-                    } else {
-                        __nv_bfloat16 t[8];
+                __nv_bfloat16* dst = &sB[buf][r][k];
+                if (n < N && vecW && k0 + k + 7 < K) {
+                    cp_async16(dst, W + (size_t)n * K + k0 + k);
+                } else {
+                    __align__(16) __nv_bfloat16 t[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) t[j] = (k0 + k + j < K) ? src[j] : __float2bfloat16(0.f);
-                        q = *reinterpret_cast<const uint4*>(t);
-                    }
+                    for (int j = 0; j < 8; ++j) t[j] = (n < N && k0 + k + j < K) ? W[(size_t)n * K + k0 + k + j] : __float2bfloat16(0.f);
+                    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(t);
                 }
-                *reinterpret_cast<uint4*>(&sB[r][k]) = q;
+            }
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+        };
+        const int nslab = (K + LIN_BK - 1) / LIN_BK;
+        stage(0, 0);
+        for (int sl = 0; sl < nslab; ++sl) {
+            const int buf = sl & 1;
+            if (sl + 1 < nslab) {
+                stage(buf ^ 1, (sl + 1) * LIN_BK);
+                asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;\n" ::: "memory");
             }
             __syncthreads();
 #pragma unroll
@@ -205,16 +225,16 @@ __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     const int r = wm + i * 16 + gq;
-                    a[i][0] = *reinterpret_cast<const uint32_t*>(&sA[r][kk + tq * 2]);
-                    a[i][1] = *reinterpret_cast<const uint32_t*>(&sA[r + 8][kk + tq * 2]);
-                    a[i][2] = *reinterpret_cast<const uint32_t*>(&sA[r][kk + 8 + tq * 2]);
-                    a[i][3] = *reinterpret_cast<const uint32_t*>(&sA[r + 8][kk + 8 + tq * 2]);
+                    a[i][0] = pack_bf16x2(*reinterpret_cast<const float2*>(&sA[buf][r][kk + tq * 2]));
+                    a[i][1] = pack_bf16x2(*reinterpret_cast<const float2*>(&sA[buf][r + 8][kk + tq * 2]));
+                    a[i][2] = pack_bf16x2(*reinterpret_cast<const float2*>(&sA[buf][r][kk + 8 + tq * 2]));
+                    a[i][3] = pack_bf16x2(*reinterpret_cast<const float2*>(&sA[buf][r + 8][kk + 8 + tq * 2]));
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int n = wn + j * 8 + gq;
-                    b[j][0] = *reinterpret_cast<const uint32_t*>(&sB[n][kk + tq * 2]);
-                    b[j][1] = *reinterpret_cast<const uint32_t*>(&sB[n][kk + 8 + tq * 2]);
+                    b[j][0] = *reinterpret_cast<const uint32_t*>(&sB[buf][n][kk + tq * 2]);
+                    b[j][1] = *reinterpret_cast<const uint32_t*>(&sB[buf][n][kk + 8 + tq * 2]);
                 }
 #pragma unroll
                 for (int i = 0; i < 2; ++i)
@@ -314,6 +334,93 @@ __global__ void __launch_bounds__(LIN_SK_WARPS * 32) lin_skinny_kernel(const Lin
 #pragma unroll
             for (int i = 0; i < LIN_SK_ROWS; ++i)
                 if (i < nr) lin_store(p, g, base + rb + i, n, a0[i], a1[i], has1);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// steps of up to 16 rows on the tensor cores: 8 outputs per CTA, the k range split over 8 warps.  A lane streams 16 bytes of
+// one weight row (8 consecutive k) and the matching 8 activations of rows g and g + 8 straight from global memory; those 8 k
+// feed two m16n8k16 products (any fixed pairing of k between the A and B fragments is a valid sum order), so no operand
+// passes through shared memory and every weight byte is read once, in full 32-byte sectors.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int LIN_M16_WARPS = 8;
+
+__device__ __forceinline__ void lin_ld8(const float* p, bool vec, int valid, float v[8]) {
+    if (vec && valid >= 8) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p + 4));
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = j < valid ? p[j] : 0.f;
+    }
+}
+
+__global__ void __launch_bounds__(LIN_M16_WARPS * 32) lin_mma16_kernel(const LinParams p) {
+    const int g = blockIdx.z;
+    const int rows = p.cnt[(size_t)g * p.cnt_gstride];
+    if (rows <= 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    const int n0 = blockIdx.x * 8;
+    const int base = p.off ? p.off[g] : 0;
+    const float* X = p.X + g * p.x_gstride;
+    const int K = p.K, n = n0 + gq;
+    const __nv_bfloat16* wrow = p.W + g * p.w_gstride + (size_t)min(n, p.N - 1) * K;
+    const bool nvalid = n < p.N;
+    const bool vecW = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.W + g * p.w_gstride) & 15) == 0);
+    const bool vecX = (p.ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(X) & 15) == 0);
+    __shared__ float red[LIN_M16_WARPS][16][8];
+    for (int rb = 0; rb < rows; rb += 16) {
+        const int rlo = rb + gq, rhi = rb + gq + 8;
+        const float* xlo = rlo < rows ? X + (size_t)(p.xlist ? p.xlist[base + rlo] : base + rlo) * p.ldx : nullptr;
+        const float* xhi = rhi < rows ? X + (size_t)(p.xlist ? p.xlist[base + rhi] : base + rhi) * p.ldx : nullptr;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int kb = warp * 32; kb < K; kb += LIN_M16_WARPS * 32) {
+            const int k = kb + tq * 8;
+            const int valid = max(0, min(8, K - k));
+            uint4 wq = make_uint4(0, 0, 0, 0);
+            if (nvalid && valid > 0) {
+                if (vecW) {
+                    wq = __ldg(reinterpret_cast<const uint4*>(wrow + k));
+                } else {
+                    __align__(16) __nv_bfloat16 t[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) t[j] = j < valid ? wrow[k + j] : __float2bfloat16(0.f);
+                    wq = *reinterpret_cast<const uint4*>(t);
+                }
+            }
+            float lo[8], hi[8];
+            if (xlo && valid > 0) lin_ld8(xlo + k, vecX, valid, lo);
+            else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) lo[j] = 0.f;
+            }
+            if (xhi && valid > 0) lin_ld8(xhi + k, vecX, valid, hi);
+            else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) hi[j] = 0.f;
+            }
+            uint32_t a[4], b[2];
+            a[0] = pack_bf16x2(make_float2(lo[0], lo[1])); a[1] = pack_bf16x2(make_float2(hi[0], hi[1]));
+            a[2] = pack_bf16x2(make_float2(lo[2], lo[3])); a[3] = pack_bf16x2(make_float2(hi[2], hi[3]));
+            b[0] = wq.x; b[1] = wq.y;
+            mma_bf16_16816(acc, a, b);
+            a[0] = pack_bf16x2(make_float2(lo[4], lo[5])); a[1] = pack_bf16x2(make_float2(hi[4], hi[5]));
+            a[2] = pack_bf16x2(make_float2(lo[6], lo[7])); a[3] = pack_bf16x2(make_float2(hi[6], hi[7]));
+            b[0] = wq.z; b[1] = wq.w;
+            mma_bf16_16816(acc, a, b);
+        }
+        __syncthreads();                           // red of the previous row block has been read
+        red[warp][gq][tq * 2] = acc[0]; red[warp][gq][tq * 2 + 1] = acc[1];
+        red[warp][gq + 8][tq * 2] = acc[2]; red[warp][gq + 8][tq * 2 + 1] = acc[3];
+        __syncthreads();
+        if (threadIdx.x < 64) {
+            const int r = threadIdx.x >> 2, c = (threadIdx.x & 3) * 2;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < LIN_M16_WARPS; ++w) { s0 += red[w][r][c]; s1 += red[w][r][c + 1]; }
+            if (rb + r < rows && n0 + c < p.N) lin_store(p, g, base + rb + r, n0 + c, s0, s1, n0 + c + 1 < p.N);
         }
     }
 }

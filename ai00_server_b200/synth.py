@@ -320,8 +320,10 @@ def kemirax_layer(kind: str, *, heads=4, dim=16, vdim=16, rot_dim=8, kv_rank=24,
     return layer
 
 
-def make_kemirax(layers: list, width: int = 64, vocab: int = 96, eps: float = 1e-5, seed: int = 0, gain: float = 1.0, a_rank: int = 8):
-    """(config.json bytes, safetensors image, dict of float32 arrays rounded to bf16) for a random model of the family."""
+def make_kemirax(layers: list, width: int = 64, vocab: int = 96, eps: float = 1e-5, seed: int = 0, gain: float = 1.0, a_rank: int = 8,
+                 arrays: bool = True):
+    """(config.json bytes, safetensors image, dict of float64 arrays holding the bf16-rounded values, or None when `arrays` is
+    off) for a random model of the family."""
     rng = np.random.default_rng(seed)
     W = width
     t = {}
@@ -377,6 +379,8 @@ def make_kemirax(layers: list, width: int = 64, vocab: int = 96, eps: float = 1e
     t["final.norm"] = np.float32(rng.uniform(0.8, 1.2))
     t["head"] = mat(vocab, W)
     cfg = {"architecture": "Kemirax", "layers": layers, "norm": {"eps": eps}, "vocab": vocab, "width": W}
+    if not arrays:
+        return json.dumps(cfg).encode(), pack_st_bf16(t), None
     bits = {k: to_bf16_bits(np.asarray(v, np.float32).reshape(np.shape(v))) for k, v in t.items()}
     rounded = {k: (b.astype(np.uint32) << 16).view(np.float32).reshape(np.shape(t[k])).astype(np.float64) for k, b in bits.items()}
     return json.dumps(cfg).encode(), pack_st_bf16(t), rounded

@@ -280,6 +280,96 @@ def prefill_main(args):
     model.close()
 
 
+KX_SIZES = {
+    # width, layers (latent, borrowed-cache latent, gla, latent), heads, dim, rot, vdim, kv_rank, q_rank, experts x ff, top, shared ff, vocab
+    "w1024": dict(width=1024, heads=8, dim=128, rot_dim=64, vdim=128, kv_rank=256, q_rank=384, experts=8, ff=512, top=2, shared_ff=1024, vocab=32768),
+    "w2048": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, experts=16, ff=1024, top=4, shared_ff=2048, vocab=32768),
+}
+
+
+def kemirax_main(args):
+    """Prefill and decode throughput of the Kemirax family beside an RWKV-7 stack of equal width, depth and vocabulary."""
+    from ai00_server_b200 import capi, runtime, synth
+    peaks, peak_kind = read_peaks()
+    hbm, tf = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
+    B, ctx, plen = args.batch, args.context, args.seq_len
+    rng = np.random.default_rng(7)
+
+    def time_arm(m, vocab, reset):
+        slots = list(range(B))
+        for s_ in slots:
+            reset(s_)
+        prompt = rng.integers(1, vocab, size=(B, max(ctx, 1)))
+        # prefill: every sequence's prompt through the public infer call (token ids from the host, last row back), timed on the host
+        # around the synchronous call; the first call also captures the step graphs, so it is repeated
+        best = None
+        for rep in range(3):
+            for s_ in slots:
+                reset(s_)
+            t0 = time.perf_counter()
+            m.infer_raw(slots, [ctx] * B, [int(t) for r in prompt for t in r], [capi.OPTION_LAST] * B)
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        toks = rng.integers(1, vocab, size=(args.warmup + args.steps, B)).astype(np.uint32)
+        ms, launches = m.bench_decode(slots, toks, args.warmup, args.steps)
+        cls_ms, cls_n, _ = m.profile_step(slots, toks[0])
+        return {"prefill_tokens_per_s": B * ctx / best, "prefill_s": best, "decode_tokens_per_s": B * args.steps / (ms * 1e-3),
+                "decode_ms_per_step": ms / args.steps, "launches_per_step": launches / args.steps,
+                "ungraphed_step_ms_by_class": {"linear": cls_ms[0], "mixer": cls_ms[1], "norm": cls_ms[2], "other": cls_ms[3]},
+                "launches_by_class": list(cls_n)}
+
+    for name in args.kx_sizes.split(","):
+        z = KX_SIZES[name]
+        W, V = z["width"], z["vocab"]
+        att = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"], q_rank=z["q_rank"],
+                   experts=z["experts"], identity=2, top=z["top"], ff=z["ff"], shared_ff=z["shared_ff"],
+                   scaling={"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0})
+        gla = dict(heads=z["heads"], dim=z["dim"], vdim=z["vdim"], experts=z["experts"], identity=2, top=z["top"], ff=z["ff"], shared_ff=z["shared_ff"])
+        layers = [synth.kemirax_layer("latent_attention", **att), synth.kemirax_layer("latent_attention", kv_from=0, **att),
+                  synth.kemirax_layer("gla", **gla), synth.kemirax_layer("latent_attention", **att)]
+        cfg, st, _ = synth.make_kemirax(layers, width=W, vocab=V, seed=1, gain=0.5, arrays=False)
+        # algorithmic work: weights one token touches (dense + top experts), weights a decode step streams (dense + the experts
+        # its B x top choices can reach), cache rows every attention layer reads
+        E, top, D = z["experts"], z["top"], z["kv_rank"] + z["rot_dim"]
+        expert = 3 * W * z["ff"]
+        H, dn, dr, dv, rk, rq = z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["kv_rank"], z["q_rank"]
+        lat = rq * W + H * (dn + dr) * rq + H * dn * rk + H * dv * rk + W * H * dv
+        dense = {"latent": lat + D * W, "borrow": lat, "gla": 2 * H * dn * W + 2 * H * dv * W + W * H * dv + 8 * W + H * dn * 8}
+        common = 2 * W * W + (E + 2) * W + 3 * W * z["shared_ff"] + W
+        per_layer_dense = [dense["latent"] + common, dense["borrow"] + common, dense["gla"] + common, dense["latent"] + common]
+        reach = min(E, B * top)
+        active = sum(per_layer_dense) + 4 * top * expert + V * W
+        step_bytes = 2 * (sum(per_layer_dense) + 4 * reach * expert + V * W) + 3 * B * ctx * D * 4
+        attn_flops_tok = 3 * 2 * H * (2 * rk + dr) * ctx / 2           # absorbed form, mean context ctx / 2 during the prompt
+        m = runtime.Model(st, max_batch=B, token_chunk_size=128, config=cfg, kv_tokens=B * (ctx + args.warmup + args.steps + 8))
+        r = time_arm(m, V, m.state.reset)
+        m.close()
+        r.update({"family": "kemirax", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(active),
+                  "decode_algorithmic_bytes_per_step": int(step_bytes),
+                  "decode_frac_of_hbm_peak": step_bytes / (r["decode_ms_per_step"] * 1e-3) / (hbm * 1e9),
+                  "prefill_tflops": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12,
+                  "prefill_frac_of_bf16_peak": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12 / tf,
+                  "peaks": peak_kind, "dtype": "bf16", "data": "synthetic"})
+        print(json.dumps(r), flush=True)
+        del st
+        # the closest existing family at equal size: RWKV-7, same width, depth and vocabulary, hidden = 4 x width
+        shp = synth.Shape(7, 4, W, 4 * W, V=V, Dd=64, Da=64, Dv=32, Dg=128)
+        st7 = synth.make_st(shp, 0)
+        m7 = runtime.Model(st7, max_batch=B, token_chunk_size=128)
+        init = m7.state.init()
+        r7 = time_arm(m7, V, lambda s_: m7.state.load(init, s_))
+        m7.close()
+        p7 = synth.num_params(shp)
+        b7 = synth.algorithmic_bytes_per_step(shp, B)
+        r7.update({"family": "rwkv7", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(p7),
+                   "decode_algorithmic_bytes_per_step": int(b7),
+                   "decode_frac_of_hbm_peak": b7 / (r7["decode_ms_per_step"] * 1e-3) / (hbm * 1e9),
+                   "prefill_tflops": 2 * p7 * r7["prefill_tokens_per_s"] / 1e12,
+                   "prefill_frac_of_bf16_peak": 2 * p7 * r7["prefill_tokens_per_s"] / 1e12 / tf,
+                   "peaks": peak_kind, "dtype": "fp16", "data": "synthetic"})
+        print(json.dumps(r7), flush=True)
+
+
 def main():
     global PRESET, BATCH
     ap = argparse.ArgumentParser()
@@ -298,8 +388,15 @@ def main():
     ap.add_argument("--quant-layers", type=int, default=-1, help="the reference's `quant`: first N layers (default: all)")
     ap.add_argument("--seqs", type=int, default=256)
     ap.add_argument("--seq-len", type=int, default=512)
+    ap.add_argument("--family", default="rwkv", choices=["rwkv", "kemirax"],
+                    help="kemirax: prefill and decode throughput of the Kemirax family at layer sizes of a real model (random weights), "
+                         "beside an RWKV-7 stack of equal width and depth; one JSON line per arm (not the headline workload)")
+    ap.add_argument("--kx-sizes", default="w1024,w2048", help="--family kemirax: comma-separated size names")
+    ap.add_argument("--context", type=int, default=1024, help="--family kemirax: tokens each sequence holds before the timed decode steps")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.family == "kemirax":
+        return kemirax_main(args)
     PRESET, BATCH = args.preset, args.batch
     METRIC = metric_name(PRESET, BATCH)
     if args.quant != "none":

@@ -56,6 +56,14 @@ def bf16_round(x):
 # ----------------------------------------------------------------------------------------------------------------------
 # small pieces
 # ----------------------------------------------------------------------------------------------------------------------
+ROUND_OPERANDS = False      # True: the activation operand of every projection is rounded to bfloat16 first (noise-floor runs)
+
+
+def lin(Wm, x):
+    """Projection Wm @ x; with ROUND_OPERANDS the activation is rounded to bfloat16 as a tensor-core operand would be."""
+    return Wm @ (bf16_round(np.asarray(x, np.float64)) if ROUND_OPERANDS else x)
+
+
 def rms_unit(x, eps):
     return x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps)
 
@@ -113,10 +121,10 @@ def latent_attention_token(w, pre, m, eps, h, pos, cache):
     """cache: list of (latent c [kv_rank], rotated shared key [rot_dim]) of positions 0..pos (this token appended by the
     layer that owns the cache before the call returns)."""
     H, dn, dr, dv, rk = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"])
-    cq = rms_unit(w[pre + "dq"] @ h, eps) * w[pre + "dq.norm"]
-    q = (w[pre + "uq"] @ cq).reshape(H, dn + dr)
+    cq = rms_unit(lin(w[pre + "dq"], h), eps) * w[pre + "dq.norm"]
+    q = lin(w[pre + "uq"], cq).reshape(H, dn + dr)
     if "kv_from" not in m:
-        kv = w[pre + "dkv"] @ h
+        kv = lin(w[pre + "dkv"], h)
         c = rms_unit(kv[:rk], eps) * w[pre + "dkv.norm"]
         kr = rotate(kv[rk:], pos, m["rot"])
         cache.append((c, kr))
@@ -133,32 +141,32 @@ def latent_attention_token(w, pre, m, eps, h, pos, cache):
         s = (K @ qn + KR @ qr) * float(m["scale"])
         p = softmax(s)
         out[hd] = p @ Vv
-    return w[pre + "o"] @ out.reshape(-1)
+    return lin(w[pre + "o"], out.reshape(-1))
 
 
 def gla_token(w, pre, m, eps, h, S):
     """S: [heads, dim, vdim] float state, updated in place."""
     H, dk, dv = int(m["heads"]), int(m["dim"]), int(m["vdim"])
-    q = (w[pre + "q"] @ h).reshape(H, dk) * dk ** -0.5
-    k = (w[pre + "k"] @ h).reshape(H, dk)
-    v = (w[pre + "v"] @ h).reshape(H, dv)
-    z = w[pre + "a2"] @ (w[pre + "a1"] @ h) + w[pre + "a2.b"]
+    q = lin(w[pre + "q"], h).reshape(H, dk) * dk ** -0.5
+    k = lin(w[pre + "k"], h).reshape(H, dk)
+    v = lin(w[pre + "v"], h).reshape(H, dv)
+    z = lin(w[pre + "a2"], lin(w[pre + "a1"], h)) + w[pre + "a2.b"]
     alpha = (sigmoid(z) ** (1.0 / float(m["tau"]))).reshape(H, dk)
     o = np.zeros((H, dv))
     for hd in range(H):
         S[hd] = alpha[hd][:, None] * S[hd] + np.outer(k[hd], v[hd])
         o[hd] = rms_unit(S[hd].T @ q[hd], eps) * w[pre + "norm"]
-    g = w[pre + "g"] @ h
-    return w[pre + "o"] @ (o.reshape(-1) * (g * sigmoid(g)))
+    g = lin(w[pre + "g"], h)
+    return lin(w[pre + "o"], o.reshape(-1) * (g * sigmoid(g)))
 
 
 # ----------------------------------------------------------------------------------------------------------------------
 # feed-forward
 # ----------------------------------------------------------------------------------------------------------------------
 def clamped_expert(w, pre, limit, h):
-    g = np.minimum(w[pre + "gate"] @ h, limit)
-    u = np.clip(w[pre + "up"] @ h, -limit, limit)
-    return w[pre + "down"] @ (g * sigmoid(1.702 * g) * (u + 1.0))
+    g = np.minimum(lin(w[pre + "gate"], h), limit)
+    u = np.clip(lin(w[pre + "up"], h), -limit, limit)
+    return lin(w[pre + "down"], g * sigmoid(1.702 * g) * (u + 1.0))
 
 
 def moe_token(w, pre, mlp, h):
@@ -206,16 +214,16 @@ def step_token(cfg, w, seq: Sequence, token: int, layers_out=None):
             a = gla_token(w, p + "mix.", m, eps, hs, seq.S[i])
         else:
             raise ValueError(l["type"])
-        a = a * sigmoid(w[p + "rg1"] @ h + w[p + "rg1.b"])
+        a = a * sigmoid(lin(w[p + "rg1"], h) + w[p + "rg1.b"])
         if l.get("mlp"):
-            f = moe_token(w, p + "mlp.", l["mlp"], h) * sigmoid(w[p + "rg2"] @ h + w[p + "rg2.b"])
+            f = moe_token(w, p + "mlp.", l["mlp"], h) * sigmoid(lin(w[p + "rg2"], h) + w[p + "rg2.b"])
             x = x + (a + f)
         else:
             x = x + a
         if layers_out is not None:
             layers_out.append(x.copy())
     seq.pos += 1
-    return w["head"] @ (rms_unit(x, eps) * float(w["final.norm"]))
+    return lin(w["head"], rms_unit(x, eps) * float(w["final.norm"]))
 
 
 def run(cfg, w, tokens, seq: Sequence | None = None, layers=False):

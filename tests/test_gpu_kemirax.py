@@ -1,7 +1,7 @@
 """GPU tests of the Kemirax family: the CUDA engine (through runtime.Model, i.e. the C ABI's infer / state / sampling entry
 points and its own step packing) against the plain NumPy restatement in oracle/kemirax_numpy.py, on small random models
 made here.  precision 1 (every product in f32) is held to a tight bound, precision 0 (bf16 tensor-core products for
-multi-token steps) to the bf16 rounding level.
+multi-token steps) to three times the restatement's own bf16 operand-rounding error.
 """
 import json
 
@@ -14,17 +14,38 @@ from oracle import kemirax_numpy as K
 pytestmark = pytest.mark.gpu
 
 TIGHT = 2e-4        # f32 engine vs float64 oracle, relative to the logits' spread
-LOOSE = 6e-2        # bf16 operand rounding through a few layers
 
 YARN = {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}
 LA = synth.kemirax_layer
 
 
-def err(got, want):
+def row_errs(got, want):
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     d = got - want
     d = d - d.mean(-1, keepdims=True)
-    return float(np.sqrt((d ** 2).mean(-1)).max() / np.sqrt(((want - want.mean(-1, keepdims=True)) ** 2).mean()))
+    return np.sqrt((d ** 2).mean(-1)) / np.sqrt(((want - want.mean(-1, keepdims=True)) ** 2).mean())
+
+
+def err(got, want):
+    return float(row_errs(got, want).max())
+
+
+def bf16_floor(b, toks, want):
+    """Per row, how far the restatement itself moves when every projection's activation operand is rounded to bfloat16: the
+    yardstick for precision 0, whose multi-token steps round exactly those operands (its one-token steps round nothing)."""
+    K.ROUND_OPERANDS = True
+    try:
+        return row_errs(b.oracle(toks), want)
+    finally:
+        K.ROUND_OPERANDS = False
+
+
+def assert_serving(got, want, floor):
+    """Typical rows sit at the rounding floor; a rare row may sit far above it, where operand rounding flips a close router
+    decision (the restatement's own rounded run has such rows too, at other places), so rows are counted, not maximised."""
+    e = row_errs(got, want)
+    assert np.median(e) <= 2.0 * np.median(floor)
+    assert (e > 3.0 * floor.max()).sum() <= max(1, 0.02 * len(e))
 
 
 class Bundle:
@@ -232,10 +253,14 @@ def test_other_sizes(precision):
     try:
         toks = b.tokens(45, 2)
         want = b.oracle(toks)
-        tol = TIGHT if precision else LOOSE
-        assert err(b.feed(0, toks), want) <= tol
-        out = [b.feed(1, toks[:9])] + [b.feed(1, [t], capi.OPTION_LAST) for t in toks[9:20]] + [b.feed(1, toks[20:])]
-        assert err(np.concatenate(out), want) <= tol
+        whole = b.feed(0, toks)
+        cut = np.concatenate([b.feed(1, toks[:9])] + [b.feed(1, [t], capi.OPTION_LAST) for t in toks[9:20]] + [b.feed(1, toks[20:])])
+        if precision:
+            assert err(whole, want) <= TIGHT and err(cut, want) <= TIGHT
+        else:
+            floor = bf16_floor(b, toks, want)
+            assert_serving(whole, want, floor)
+            assert_serving(cut, want, floor)
     finally:
         b.close()
 
@@ -244,10 +269,11 @@ def test_serving_precision(stack_ref):
     b = Bundle(STACK, precision=0)
     try:
         toks, want = stack_ref
-        whole = b.feed(0, toks)
-        assert err(whole, want) <= LOOSE
+        floor = bf16_floor(b, toks, want)
+        assert 1e-4 < np.median(floor) < 0.1
+        assert_serving(b.feed(0, toks), want, floor)
         out = [b.feed(1, toks[:37])] + [b.feed(1, [t], capi.OPTION_LAST) for t in toks[37:60]] + [b.feed(1, toks[60:])]
-        assert err(np.concatenate(out), want) <= LOOSE
+        assert_serving(np.concatenate(out), want, floor)
     finally:
         b.close()
 
