@@ -29,14 +29,21 @@ __global__ void gla_kernel(const GlaParams p) {
     if (si >= p.meta.nslots()) return;
     const int slot = p.meta.slot_id()[si], t0 = p.meta.slot_start()[si], nt = p.meta.slot_count()[si];
     const int dk = p.dk, dv = p.dv, j = threadIdx.x;
-    extern __shared__ float gla_smem[];
+    extern __shared__ __align__(16) float gla_smem[];
     float* S = gla_smem;                             // [dk][dv]
     float* sq = S + (size_t)dk * dv;              // [dk]
     float* skk = sq + dk;
     float* sa = skk + dk;
     float* red = sa + dk;                         // [32]
     float* gS = p.state + ((size_t)slot * p.H + h) * dk * dv;
-    for (int e = j; e < dk * dv; e += blockDim.x) S[e] = gS[e];
+    const int nst = dk * dv;
+    const bool vec = (nst % 4) == 0;                  // slot records then start on 16-byte boundaries
+    if (vec) {
+#pragma unroll 8
+        for (int e = j; e < nst / 4; e += blockDim.x) reinterpret_cast<float4*>(S)[e] = __ldg(reinterpret_cast<const float4*>(gS) + e);
+    } else {
+        for (int e = j; e < nst; e += blockDim.x) S[e] = gS[e];
+    }
     for (int t = t0; t < t0 + nt; ++t) {
         __syncthreads();
         for (int i = j; i < dk; i += blockDim.x) {
@@ -72,7 +79,12 @@ __global__ void gla_kernel(const GlaParams p) {
         }
     }
     __syncthreads();
-    for (int e = j; e < dk * dv; e += blockDim.x) gS[e] = S[e];
+    if (vec) {
+#pragma unroll 8
+        for (int e = j; e < nst / 4; e += blockDim.x) reinterpret_cast<float4*>(gS)[e] = reinterpret_cast<const float4*>(S)[e];
+    } else {
+        for (int e = j; e < nst; e += blockDim.x) gS[e] = S[e];
+    }
 }
 
 }  // namespace b200

@@ -257,6 +257,9 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
         CK(cudaFuncSetAttribute(latent_attn_tc_kernel<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tc));
     }
     CK(cudaFuncSetAttribute(gla_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    CK(cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
+    REQUIRE(moe_route_smem(W, 2048) <= 128 * 1024, B200RWKV_ERR_UNSUPPORTED, "width too large for the router kernel");
+    CK(cudaFuncSetAttribute(lin_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LIN_TC_SMEM));
     CK(cudaDeviceSynchronize());
 }
 
@@ -271,7 +274,7 @@ void b200rwkv_engine::kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int ro
     } else if (exact) {
         launch_k(lin_tile_kernel<true>, dim3(cdiv(p.N, LIN_BN), cdiv(rows, LIN_BM), groups), dim3(LIN_THREADS), 0, p, KC_GEMM, s, prof);
     } else {
-        launch_k(lin_tile_kernel<false>, dim3(cdiv(p.N, LIN_BN), cdiv(rows, LIN_BM), groups), dim3(LIN_THREADS), 0, p, KC_GEMM, s, prof);
+        launch_k(lin_tile_kernel<false>, dim3(cdiv(p.N, LIN_BN), cdiv(rows, LIN_BM), groups), dim3(LIN_THREADS), LIN_TC_SMEM, p, KC_GEMM, s, prof);
     }
 }
 
@@ -359,11 +362,10 @@ void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool 
         }
         if (c.has_mlp) {
             const int E = c.experts, NE = E + c.identity, ff = c.ff;
-            kx_lin(s, prof, lin(m.h, W, l.router, m.rl, NE, NE, W), rows, 1, true);           // router logits in f32 in every mode
-            MoeRouteParams rp{m.rl, NE, l.corr, NE, c.top, m.sel, m.wgt, mv};
-            launch_k(moe_route_kernel, dim3(cdiv(rows, 4)), dim3(128), 0, rp, KC_OTHER, s, prof);
+            MoeRouteParams rp{m.h, W, l.router, W, l.corr, NE, c.top, m.sel, m.wgt, mv};
+            launch_k(moe_route_kernel, dim3(rows), dim3(MOE_ROUTE_THREADS), moe_route_smem(W, NE), rp, KC_OTHER, s, prof);
             MoeGroupParams gp{m.sel, c.top, E, m.cnt, m.off, m.list, m.row_of, mv};
-            launch_k(moe_group_kernel, dim3(1), dim3(256), (size_t)std::max(E, 1) * 8, gp, KC_OTHER, s, prof);
+            launch_k(moe_group_kernel, dim3(1), dim3(256), ((size_t)std::max(E, 1) * 2 + (size_t)maxT * c.top) * 4, gp, KC_OTHER, s, prof);
             if (E > 0) {
                 LinParams p1 = lin(m.h, W, l.gu, m.yc, ff, 2 * ff, W, LE_GLU_CLAMP);
                 p1.w_gstride = (long long)2 * ff * W; p1.cnt = m.cnt; p1.cnt_gstride = 1; p1.off = m.off; p1.xlist = m.list; p1.limit = c.limit;
@@ -441,7 +443,7 @@ void b200rwkv_engine::kx_fill_step(int* hm, const std::vector<int>& slots, const
     int ns = 1;
     if (hg_min < (1 << 30)) {
         const int ctas = std::max(1, nch * hg_min), tiles = cdiv(ctx_max, LA_KT);
-        while (ns < m.max_split && ctas * ns < 2 * num_sms && tiles / (ns * 2) >= 4) ns *= 2;
+        while (ns < m.max_split && ctas * ns < 2 * num_sms && tiles / (ns * 2) >= 2) ns *= 2;
     }
     *decode = dec; *nsplit = ns;
 }
@@ -544,7 +546,7 @@ void b200rwkv_engine::kx_xfer(int slot, float* rec, int ctx_rows, bool import, i
 // host copy between two records of the same model whose cache blocks have different row counts
 static void kx_relayout(const Kemirax& m, const float* src, int src_rows, float* dst, int dst_rows, int n) {
     size_t a = 4, b = 4;
-    memcpy(dst, src, 16);
+    memset(dst, 0, 16);                                    // header: the caller writes the token count
     for (const KxLayer& l : m.layers) {
         memcpy(dst + b, src + a, (size_t)m.W * 4); a += m.W; b += m.W;
         if (l.c.mixer == KX_GLA) {

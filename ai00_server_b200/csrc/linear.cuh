@@ -78,6 +78,8 @@ __device__ __forceinline__ void lin_store(const LinParams& p, int g, int yrow, i
 // tiled kernel: 64 rows x 64 outputs per CTA, k in slabs of 32; 128 threads
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int LIN_BM = 64, LIN_BN = 64, LIN_BK = 32, LIN_THREADS = 128;
+constexpr int LIN_TC_BK = 64, LIN_TC_STAGES = 3;       // tensor-core path: k slab and pipeline depth
+constexpr size_t LIN_TC_SMEM = (size_t)LIN_TC_STAGES * (LIN_BM * (LIN_TC_BK + 4) * sizeof(float) + LIN_BN * (LIN_TC_BK + 8) * 2);
 
 __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], const uint32_t b[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -156,12 +158,14 @@ __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p
             }
         }
     } else {
-        // two-stage cp.async pipeline: slab i+1 streams into the other buffer while slab i is multiplied.  Activations are
+        // three-stage cp.async pipeline over k slabs of 64: two slabs stream in while one is multiplied.  Activations are
         // staged as f32 and rounded to bf16 when the fragments are built; weights are staged as stored.
-        constexpr int LDA = LIN_BK + 4;                // floats: 144-byte rows (16-byte aligned chunks, spread banks)
-        constexpr int LDB = LIN_BK + 8;                // bf16: 80-byte rows
-        __shared__ __align__(16) float sA[2][LIN_BM][LDA];
-        __shared__ __align__(16) __nv_bfloat16 sB[2][LIN_BN][LDB];
+        constexpr int LDA = LIN_TC_BK + 4;             // floats: 272-byte rows (16-byte aligned chunks, spread banks)
+        constexpr int LDB = LIN_TC_BK + 8;             // bf16: 144-byte rows
+        extern __shared__ __align__(16) unsigned char lin_dyn_smem[];
+        float (*sA)[LIN_BM][LDA] = reinterpret_cast<float (*)[LIN_BM][LDA]>(lin_dyn_smem);
+        __nv_bfloat16 (*sB)[LIN_BN][LDB] =
+            reinterpret_cast<__nv_bfloat16 (*)[LIN_BN][LDB]>(lin_dyn_smem + sizeof(float) * LIN_TC_STAGES * LIN_BM * LDA);
         const int warp = tid >> 5, lane = tid & 31;
         const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;      // 2 x 2 warps, 32 x 32 each
         const int gq = lane >> 2, tq = lane & 3;
@@ -176,8 +180,8 @@ __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p
         const bool vecX = (p.ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(X) & 15) == 0);
         __syncthreads();
         auto stage = [&](int buf, int k0) {
-            for (int e = tid; e < LIN_BM * (LIN_BK / 4); e += LIN_THREADS) {
-                const int r = e / (LIN_BK / 4), k = (e % (LIN_BK / 4)) * 4;
+            for (int e = tid; e < LIN_BM * (LIN_TC_BK / 4); e += LIN_THREADS) {
+                const int r = e / (LIN_TC_BK / 4), k = (e % (LIN_TC_BK / 4)) * 4;
                 const int xr = s_xrow[r];
                 float* dst = &sA[buf][r][k];
                 if (xr >= 0 && vecX && k0 + k + 3 < K) {
@@ -193,8 +197,8 @@ __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p
                     *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
                 }
             }
-            for (int e = tid; e < LIN_BN * (LIN_BK / 8); e += LIN_THREADS) {
-                const int r = e / (LIN_BK / 8), k = (e % (LIN_BK / 8)) * 8;
+            for (int e = tid; e < LIN_BN * (LIN_TC_BK / 8); e += LIN_THREADS) {
+                const int r = e / (LIN_TC_BK / 8), k = (e % (LIN_TC_BK / 8)) * 8;
                 const int n = n0 + r;
                 __nv_bfloat16* dst = &sB[buf][r][k];
                 if (n < N && vecW && k0 + k + 7 < K) {
@@ -208,19 +212,21 @@ __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p
             }
             asm volatile("cp.async.commit_group;\n" ::: "memory");
         };
-        const int nslab = (K + LIN_BK - 1) / LIN_BK;
-        stage(0, 0);
+        const int nslab = (K + LIN_TC_BK - 1) / LIN_TC_BK;
+        // one commit group per slab, empty past the end, so that "all but the two newest groups" always means slab sl
+        for (int i = 0; i < LIN_TC_STAGES - 1; ++i) {
+            if (i < nslab) stage(i, i * LIN_TC_BK);
+            else asm volatile("cp.async.commit_group;\n" ::: "memory");
+        }
         for (int sl = 0; sl < nslab; ++sl) {
-            const int buf = sl & 1;
-            if (sl + 1 < nslab) {
-                stage(buf ^ 1, (sl + 1) * LIN_BK);
-                asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-            } else {
-                asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-            }
+            const int buf = sl % LIN_TC_STAGES;
+            // the buffer refilled here was multiplied in iteration sl - 1, which ended with a barrier
+            if (sl + LIN_TC_STAGES - 1 < nslab) stage((sl + LIN_TC_STAGES - 1) % LIN_TC_STAGES, (sl + LIN_TC_STAGES - 1) * LIN_TC_BK);
+            else asm volatile("cp.async.commit_group;\n" ::: "memory");
+            asm volatile("cp.async.wait_group %0;\n" ::"n"(LIN_TC_STAGES - 1) : "memory");
             __syncthreads();
 #pragma unroll
-            for (int kk = 0; kk < LIN_BK; kk += 16) {
+            for (int kk = 0; kk < LIN_TC_BK; kk += 16) {
                 uint32_t a[2][4], b[4][2];
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {

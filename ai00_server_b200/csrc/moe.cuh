@@ -1,5 +1,6 @@
 // Routed mixture of experts around the grouped linear kernels (linear.cuh).
-//   moe_route_kernel     one warp per token: probabilities = softmax over all router outputs (real + identity experts, f32);
+//   moe_route_kernel     one CTA per token: router logits (f32 products on the f32 row, in every precision), probabilities =
+//                        softmax over all router outputs (real + identity experts);
 //                        the `top` largest of (probability + selection bias) are chosen (ties: lower index), their weights
 //                        are the un-biased probabilities, not renormalised
 //   moe_group_kernel     one CTA: per-expert row counts, offsets and token lists in token order (deterministic), and for every
@@ -8,6 +9,7 @@
 //                                              + sigmoid(sg . h[t]) * shared[t] )                     (residual accumulate, f32)
 // The experts' matrices are stacked [E][...] so that one grouped launch covers all of them; rows are gathered by list.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math_constants.h>
 #include "common.cuh"
@@ -17,7 +19,9 @@ namespace b200 {
 constexpr int MOE_MAX_TOP = 8;
 
 struct MoeRouteParams {
-    const float* logits; int ld;              // [T, NE]
+    const float* h; int ldh;                  // [T, K] router input (f32)
+    const __nv_bfloat16* Wr;                  // [NE, K] router matrix
+    int K;
     const float* bias;                        // [NE] selection bias (nullptr: none)
     int NE, top;
     int* sel;                                 // [T][top] expert index
@@ -25,10 +29,44 @@ struct MoeRouteParams {
     MetaView meta;
 };
 
-__global__ void __launch_bounds__(128) moe_route_kernel(const MoeRouteParams p) {
-    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+constexpr int MOE_ROUTE_THREADS = 256;
+__host__ __device__ inline size_t moe_route_smem(int K, int NE) { return ((size_t)K + NE) * sizeof(float); }
+
+// One CTA per token: router logits in f32 on the f32 row (every warp takes outputs warp, warp + 8, ...), then warp 0 turns them
+// into the choice: softmax, + selection bias, `top` largest, weights = the unbiased probabilities.
+__global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const MoeRouteParams p) {
+    extern __shared__ __align__(16) float moe_route_sm[];
+    float* sh = moe_route_sm;                 // [K]
+    float* z = sh + p.K;                      // [NE]
+    const int t = blockIdx.x;
     if (t >= p.meta.T()) return;
-    const float* z = p.logits + (size_t)t * p.ld;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, K = p.K;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) sh[k] = p.h[(size_t)t * p.ldh + k];
+    __syncthreads();
+    const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.Wr) & 15) == 0);
+    for (int e = warp; e < p.NE; e += MOE_ROUTE_THREADS / 32) {
+        const __nv_bfloat16* w = p.Wr + (size_t)e * K;
+        float acc = 0.f;
+        if (vec) {
+            for (int k = lane * 8; k < K; k += 256) {
+                const uint4 q = __ldg(reinterpret_cast<const uint4*>(w + k));
+                const __nv_bfloat162* hq = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(hq[j]);
+                    acc = fmaf(f.x, sh[k + 2 * j], acc);
+                    acc = fmaf(f.y, sh[k + 2 * j + 1], acc);
+                }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) acc = fmaf(__bfloat162float(w[k]), sh[k], acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) z[e] = acc;
+    }
+    __syncthreads();
+    if (warp != 0) return;
     float mx = -CUDART_INF_F;
     for (int e = lane; e < p.NE; e += 32) mx = fmaxf(mx, z[e]);
 #pragma unroll
@@ -68,13 +106,16 @@ struct MoeGroupParams {
 };
 
 __global__ void __launch_bounds__(256) moe_group_kernel(const MoeGroupParams p) {
-    extern __shared__ int moe_s_cnt[];
-    int* s_cnt = moe_s_cnt;            // [E] counts, then [E] offsets
+    extern __shared__ int moe_smem[];         // [E] counts, [E] offsets, [T * top] choices
+    int* s_cnt = moe_smem;
     int* s_off = s_cnt + p.E;
+    int* s_sel = s_off + p.E;
     const int T = p.meta.T(), n = T * p.top;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s_sel[i] = p.sel[i];
+    __syncthreads();
     for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
         int c = 0;
-        for (int i = 0; i < n; ++i) c += (p.sel[i] == e);
+        for (int i = 0; i < n; ++i) c += (s_sel[i] == e);
         s_cnt[e] = c;
     }
     __syncthreads();
@@ -88,10 +129,10 @@ __global__ void __launch_bounds__(256) moe_group_kernel(const MoeGroupParams p) 
         p.off[e] = s_off[e];
         int w = s_off[e];
         for (int i = 0; i < n; ++i)
-            if (p.sel[i] == e) { p.list[w] = i / p.top; p.row_of[i] = w; ++w; }
+            if (s_sel[i] == e) { p.list[w] = i / p.top; p.row_of[i] = w; ++w; }
     }
     for (int i = threadIdx.x; i < n; i += blockDim.x)
-        if (p.sel[i] >= p.E) p.row_of[i] = -1;
+        if (s_sel[i] >= p.E) p.row_of[i] = -1;
 }
 
 struct MoeCombineParams {
