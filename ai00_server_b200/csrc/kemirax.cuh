@@ -243,6 +243,7 @@ struct Kemirax {
           *olat = nullptr, *vout = nullptr, *pr = nullptr, *z = nullptr, *rl = nullptr, *wgt = nullptr, *yc = nullptr, *dn = nullptr, *ys = nullptr,
           *ds = nullptr, *hn = nullptr;
     int *sel = nullptr, *cnt = nullptr, *off = nullptr, *list = nullptr, *row_of = nullptr;
+    float* lin_ws = nullptr; size_t lin_ws_floats = 0;
     float* dbg_layers = nullptr;                  // [L][maxT][W] residual after every layer (bring-up aid; nullptr: off)
     int max_split = 16;
     SeqMeta sm{nullptr, 0};

@@ -222,6 +222,8 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
     m.olat = fa(T_ * n_olat); m.vout = fa(T_ * n_vout); m.pr = fa(T_ * n_pr); m.z = fa(T_ * n_z);
     m.rl = fa(T_ * n_rl); m.wgt = fa(T_ * max_top); m.yc = fa(T_ * max_top * n_yc); m.dn = fa(T_ * max_top * W);
     m.ys = fa(T_ * n_ys); m.ds = fa(T_ * W);
+    m.lin_ws_floats = (size_t)4 << 20;                   // split-k partial sums of one projection launch
+    m.lin_ws = fa(m.lin_ws_floats);
     m.sel = (int*)dalloc(T_ * max_top * 4); m.row_of = (int*)dalloc(T_ * max_top * 4); m.list = (int*)dalloc(T_ * max_top * 4);
     m.cnt = (int*)dalloc((size_t)max_E * 4); m.off = (int*)dalloc((size_t)max_E * 4);
     d_hidden = fa(T_ * W);
@@ -274,7 +276,13 @@ void b200rwkv_engine::kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int ro
     } else if (exact) {
         launch_k(lin_tile_kernel<true>, dim3(cdiv(p.N, LIN_BN), cdiv(rows, LIN_BM), groups), dim3(LIN_THREADS), 0, p, KC_GEMM, s, prof);
     } else {
-        launch_k(lin_tile_kernel<false>, dim3(cdiv(p.N, LIN_BN), cdiv(rows, LIN_BM), groups), dim3(LIN_THREADS), LIN_TC_SMEM, p, KC_GEMM, s, prof);
+        const int ctas = cdiv(p.N, LIN_BN) * cdiv(rows, LIN_BM), nslab = cdiv(p.K, LIN_TC_BK);
+        int ks = 1;
+        if (groups == 1 && !p.off && !p.xlist && p.cnt_gstride == 0)
+            while (ks < 8 && ctas * ks * 2 <= num_sms && nslab / (ks * 2) >= 4 && (size_t)ks * 2 * rows * p.N <= kx->lin_ws_floats) ks *= 2;
+        if (ks > 1) { p.ksplit = ks; p.ws = kx->lin_ws; }
+        launch_k(lin_tile_kernel<false>, dim3(cdiv(p.N, LIN_BN) * ks, cdiv(rows, LIN_BM), groups), dim3(LIN_THREADS), LIN_TC_SMEM, p, KC_GEMM, s, prof);
+        if (ks > 1) launch_k(lin_splitk_finish_kernel, dim3(cdiv(p.N, 512), rows), dim3(256), 0, p, KC_GEMM, s, prof);
     }
 }
 

@@ -43,6 +43,11 @@ struct LinParams {
     float limit;                                       // LE_GLU_CLAMP
     int epi;
     int max_rows;                                      // upper bound of any group's rows (grid sizing)
+    // split-k (tensor-core tile kernel, one group): blockIdx.x = split * n_tiles + n_tile, split s multiplies its own range of
+    // k slabs and leaves raw sums in ws[s][max_rows][N]; lin_splitk_finish_kernel adds the splits in order and runs the epilogue.
+    // Projections with few output tiles (low-rank stages) otherwise occupy a handful of SMs, each waiting on its own loads.
+    int ksplit;                                        // 0 / 1: off
+    float* ws;
 };
 
 __device__ __forceinline__ float lin_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
@@ -102,7 +107,9 @@ __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p
     const int rows = p.cnt[(size_t)g * p.cnt_gstride];
     const int r0 = blockIdx.y * LIN_BM;
     if (r0 >= rows) return;
-    const int n0 = blockIdx.x * LIN_BN;
+    const int n_tiles = (p.N + LIN_BN - 1) / LIN_BN;
+    const int n0 = (blockIdx.x % n_tiles) * LIN_BN;
+    const int split = blockIdx.x / n_tiles;            // 0 unless split-k
     const int base = p.off ? p.off[g] : 0;
     const float* X = p.X + g * p.x_gstride;
     const __nv_bfloat16* W = p.W + g * p.w_gstride;
@@ -212,16 +219,20 @@ __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p
             }
             asm volatile("cp.async.commit_group;\n" ::: "memory");
         };
-        const int nslab = (K + LIN_TC_BK - 1) / LIN_TC_BK;
+        const int nslab_all = (K + LIN_TC_BK - 1) / LIN_TC_BK;
+        const int nsp = p.ksplit > 1 ? p.ksplit : 1;
+        const int per = (nslab_all + nsp - 1) / nsp;
+        const int slab0 = split * per;
+        const int nslab = max(0, min(nslab_all, slab0 + per) - slab0);
         // one commit group per slab, empty past the end, so that "all but the two newest groups" always means slab sl
         for (int i = 0; i < LIN_TC_STAGES - 1; ++i) {
-            if (i < nslab) stage(i, i * LIN_TC_BK);
+            if (i < nslab) stage(i, (slab0 + i) * LIN_TC_BK);
             else asm volatile("cp.async.commit_group;\n" ::: "memory");
         }
         for (int sl = 0; sl < nslab; ++sl) {
             const int buf = sl % LIN_TC_STAGES;
             // the buffer refilled here was multiplied in iteration sl - 1, which ended with a barrier
-            if (sl + LIN_TC_STAGES - 1 < nslab) stage((sl + LIN_TC_STAGES - 1) % LIN_TC_STAGES, (sl + LIN_TC_STAGES - 1) * LIN_TC_BK);
+            if (sl + LIN_TC_STAGES - 1 < nslab) stage((sl + LIN_TC_STAGES - 1) % LIN_TC_STAGES, (slab0 + sl + LIN_TC_STAGES - 1) * LIN_TC_BK);
             else asm volatile("cp.async.commit_group;\n" ::: "memory");
             asm volatile("cp.async.wait_group %0;\n" ::"n"(LIN_TC_STAGES - 1) : "memory");
             __syncthreads();
@@ -258,10 +269,33 @@ __global__ void __launch_bounds__(LIN_THREADS) lin_tile_kernel(const LinParams p
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
                     const int r = r0 + wm + i * 16 + gq + hrow * 8;
-                    if (r < rows) lin_store(p, g, base + r, n, acc[i][j][hrow * 2], acc[i][j][hrow * 2 + 1], n + 1 < N);
+                    if (r >= rows) continue;
+                    if (p.ksplit > 1) {
+                        float* dst = p.ws + ((size_t)split * p.max_rows + r) * N + n;
+                        dst[0] = acc[i][j][hrow * 2];
+                        if (n + 1 < N) dst[1] = acc[i][j][hrow * 2 + 1];
+                    } else {
+                        lin_store(p, g, base + r, n, acc[i][j][hrow * 2], acc[i][j][hrow * 2 + 1], n + 1 < N);
+                    }
                 }
             }
     }
+}
+
+// sums the split-k partials in split order and runs the epilogue (one group, rows in place)
+__global__ void __launch_bounds__(256) lin_splitk_finish_kernel(const LinParams p) {
+    const int r = blockIdx.y;
+    if (r >= p.cnt[0]) return;
+    const int n = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (n >= p.N) return;
+    const bool has1 = n + 1 < p.N;
+    float s0 = 0.f, s1 = 0.f;
+    for (int sp = 0; sp < p.ksplit; ++sp) {
+        const float* src = p.ws + ((size_t)sp * p.max_rows + r) * p.N + n;
+        s0 += src[0];
+        if (has1) s1 += src[1];
+    }
+    lin_store(p, 0, r, n, s0, s1, has1);
 }
 
 // ------------------------------------------------------------------------------------------------------------------

@@ -265,6 +265,26 @@ def test_other_sizes(precision):
         b.close()
 
 
+WIDE = [LA("latent_attention", heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=64, q_rank=96, experts=4, top=2, ff=48, shared_ff=64),
+        LA("gla", heads=4, dim=32, vdim=32, experts=4, top=2, ff=48, shared_ff=64)]
+
+
+@pytest.mark.parametrize("precision", [1, 0])
+def test_wide_rows_split_the_reduction(precision):
+    # a width at which multi-token projections split their k range over several CTAs and add the parts in a second launch
+    b = Bundle(WIDE, precision=precision, width=640, vocab=128, seed=13, gain=0.7)
+    try:
+        toks = b.tokens(40, 6)
+        want = b.oracle(toks)
+        got = np.concatenate([b.feed(0, toks[:33]), b.feed(0, toks[33:35]), b.feed(0, toks[35:])])
+        if precision:
+            assert err(got, want) <= TIGHT
+        else:
+            assert_serving(got, want, bf16_floor(b, toks, want))
+    finally:
+        b.close()
+
+
 def test_serving_precision(stack_ref):
     b = Bundle(STACK, precision=0)
     try:
