@@ -279,7 +279,7 @@ void b200rwkv_engine::kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int ro
         const int ctas = cdiv(p.N, LIN_BN) * cdiv(rows, LIN_BM), nslab = cdiv(p.K, LIN_TC_BK);
         int ks = 1;
         if (groups == 1 && !p.off && !p.xlist && p.cnt_gstride == 0)
-            while (ks < 8 && ctas * ks * 2 <= num_sms && nslab / (ks * 2) >= 4 && (size_t)ks * 2 * rows * p.N <= kx->lin_ws_floats) ks *= 2;
+            while (ks < 8 && ctas * ks * 2 <= 2 * num_sms && nslab / (ks * 2) >= 4 && (size_t)ks * 2 * rows * p.N <= kx->lin_ws_floats) ks *= 2;
         if (ks > 1) { p.ksplit = ks; p.ws = kx->lin_ws; }
         launch_k(lin_tile_kernel<false>, dim3(cdiv(p.N, LIN_BN) * ks, cdiv(rows, LIN_BM), groups), dim3(LIN_THREADS), LIN_TC_SMEM, p, KC_GEMM, s, prof);
         if (ks > 1) launch_k(lin_splitk_finish_kernel, dim3(cdiv(p.N, 512), rows), dim3(256), 0, p, KC_GEMM, s, prof);

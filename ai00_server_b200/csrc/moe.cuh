@@ -113,10 +113,12 @@ __global__ void __launch_bounds__(256) moe_group_kernel(const MoeGroupParams p) 
     const int T = p.meta.T(), n = T * p.top;
     for (int i = threadIdx.x; i < n; i += blockDim.x) s_sel[i] = p.sel[i];
     __syncthreads();
-    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+    // a warp per expert: ballots over 32 choices at a time keep the token order without a serial scan
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int e = warp; e < p.E; e += nw) {
         int c = 0;
-        for (int i = 0; i < n; ++i) c += (s_sel[i] == e);
-        s_cnt[e] = c;
+        for (int i0 = 0; i0 < n; i0 += 32) c += __popc(__ballot_sync(0xffffffffu, i0 + lane < n && s_sel[i0 + lane] == e));
+        if (lane == 0) s_cnt[e] = c;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -124,12 +126,20 @@ __global__ void __launch_bounds__(256) moe_group_kernel(const MoeGroupParams p) 
         for (int e = 0; e < p.E; ++e) { s_off[e] = acc; acc += s_cnt[e]; }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
-        p.cnt[e] = s_cnt[e];
-        p.off[e] = s_off[e];
+    for (int e = warp; e < p.E; e += nw) {
+        if (lane == 0) { p.cnt[e] = s_cnt[e]; p.off[e] = s_off[e]; }
         int w = s_off[e];
-        for (int i = 0; i < n; ++i)
-            if (s_sel[i] == e) { p.list[w] = i / p.top; p.row_of[i] = w; ++w; }
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < n && s_sel[i] == e;
+            const unsigned mask = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int pos = w + __popc(mask & ((1u << lane) - 1u));
+                p.list[pos] = i / p.top;
+                p.row_of[i] = pos;
+            }
+            w += __popc(mask);
+        }
     }
     for (int i = threadIdx.x; i < n; i += blockDim.x)
         if (s_sel[i] >= p.E) p.row_of[i] = -1;
