@@ -58,6 +58,9 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
     REQUIRE(world == 1, B200RWKV_ERR_UNSUPPORTED, "Kemirax models run on one GPU in this version");
     REQUIRE(quant_layers == 0 && loras.empty(), B200RWKV_ERR_UNSUPPORTED, "Kemirax models take no LoRA / quantised layers");
     use_pdl = false;                                       // these kernels carry no programmatic-dependency waits
+    // steps of up to 512 tokens when the caller's token_chunk_size asks for them (prompts then stream the weights once per 512
+    // tokens and fill the experts' row tiles); 128 otherwise, like the other families
+    maxT = chunk > 256 ? 512 : (chunk > 128 ? 256 : 128);
     CK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
     CK(cudaStreamCreateWithFlags(&sm_stream, cudaStreamNonBlocking));
     CK(cudaEventCreateWithFlags(&step_done, cudaEventDisableTiming));
@@ -403,7 +406,11 @@ void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool 
     }
 }
 
-static inline int kx_bucket(int n) { return n <= 8 ? 8 : (n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : 128))); }
+static inline int kx_bucket(int n) {
+    for (int b = 8; b < 512; b *= 2)
+        if (n <= b) return b;
+    return 512;
+}
 
 // positions, attention chunks and page-table updates of one step; hands out pages
 void b200rwkv_engine::kx_fill_step(int* hm, const std::vector<int>& slots, const std::vector<int>& counts, bool* decode, int* nsplit) {
@@ -466,7 +473,7 @@ void b200rwkv_engine::kx_run_step(int T, int R, bool decode, int nsplit) {
     }
     int lg = 0;
     while ((1 << lg) < nsplit) ++lg;
-    const int key = 1000000 + (((rows / 8) * 32 + rrows / 8) * 2 + (decode ? 1 : 0)) * 8 + lg;
+    const int key = 1000000 + (((rows / 8) * 128 + rrows / 8) * 2 + (decode ? 1 : 0)) * 8 + lg;
     auto it = graphs.find(key);
     if (it == graphs.end()) {
         cudaGraph_t g = nullptr;

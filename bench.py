@@ -341,7 +341,7 @@ def kemirax_main(args):
         active = sum(per_layer_dense) + 4 * top * expert + V * W
         step_bytes = 2 * (sum(per_layer_dense) + 4 * reach * expert + V * W) + 3 * B * ctx * D * 4
         attn_flops_tok = 3 * 2 * H * (2 * rk + dr) * ctx / 2           # absorbed form, mean context ctx / 2 during the prompt
-        m = runtime.Model(st, max_batch=B, token_chunk_size=128, config=cfg, kv_tokens=B * (ctx + args.warmup + args.steps + 8))
+        m = runtime.Model(st, max_batch=B, token_chunk_size=512, config=cfg, kv_tokens=B * (ctx + args.warmup + args.steps + 8))
         r = time_arm(m, V, m.state.reset)
         m.close()
         r.update({"family": "kemirax", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(active),

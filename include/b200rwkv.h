@@ -104,7 +104,8 @@ typedef struct {
      * attention / gated linear attention + routed experts, bf16 weights): the JSON text, borrowed during the call.  NULL: the
      * family is recognised from the tensor names (RWKV v5 / v6 / v7).  Such models keep an attention cache in pages of
      * `kv_page` tokens (0 = 64) drawn from a pool sized for `kv_tokens` tokens over all live sequences (0 = 4096 per slot);
-     * precision 0 = bf16 tensor-core products with f32 accumulation for multi-token steps, 1 = every product in plain f32. */
+     * precision 0 = bf16 tensor-core products with f32 accumulation, 1 = every product in plain f32.  Their steps hold up to
+     * 128 tokens, 256 or 512 when token_chunk_size asks for more than 128 / 256. */
     const uint8_t* config_json;
     size_t config_len;
     int32_t kv_tokens;

@@ -49,10 +49,10 @@ def assert_serving(got, want, floor):
 
 
 class Bundle:
-    def __init__(self, layers, precision=1, slots=3, kv_tokens=2048, kv_page=16, seed=0, **kw):
+    def __init__(self, layers, precision=1, slots=3, kv_tokens=2048, kv_page=16, seed=0, chunk=128, **kw):
         self.cfg_bytes, self.st, self.w = synth.make_kemirax(layers, seed=seed, **kw)
         self.cfg = json.loads(self.cfg_bytes)
-        self.m = runtime.Model(self.st, max_batch=slots, token_chunk_size=128, precision=precision, config=self.cfg_bytes,
+        self.m = runtime.Model(self.st, max_batch=slots, token_chunk_size=chunk, precision=precision, config=self.cfg_bytes,
                                kv_tokens=kv_tokens, kv_page=kv_page)
         self.vocab = self.cfg["vocab"]
 
@@ -281,6 +281,28 @@ def test_wide_rows_split_the_reduction(precision):
             assert err(got, want) <= TIGHT
         else:
             assert_serving(got, want, bf16_floor(b, toks, want))
+    finally:
+        b.close()
+
+
+@pytest.mark.parametrize("precision", [1, 0])
+def test_steps_of_up_to_512_tokens(precision, stack_ref):
+    # token_chunk_size 512: a 150-token prompt is one step, a 330-token prompt one step of the largest bucket
+    b = Bundle(STACK, precision=precision, chunk=512)
+    try:
+        toks, want = stack_ref
+        long = b.tokens(330, 21)
+        want_long = b.oracle(long)
+        got = b.feed(0, toks)
+        got_long = np.concatenate([b.feed(1, long[:300]), b.feed(1, long[300:])])
+        rows = b.m.infer_raw([0, 2], [1, 140], [5] + long[:140], [capi.OPTION_LAST, capi.OPTION_FULL])       # a mixed step
+        if precision:
+            assert err(got, want) <= TIGHT and err(got_long, want_long) <= TIGHT
+            assert err(rows[1], want_long[:140]) <= TIGHT
+            assert err(rows[0], b.oracle(toks + [5])[-1:]) <= TIGHT
+        else:
+            assert_serving(got, want, bf16_floor(b, toks, want))
+            assert_serving(got_long, want_long, bf16_floor(b, long, want_long))
     finally:
         b.close()
 
