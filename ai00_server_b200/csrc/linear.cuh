@@ -396,7 +396,7 @@ __device__ __forceinline__ void lin_ld8(const float* p, bool vec, int valid, flo
     }
 }
 
-__global__ void __launch_bounds__(LIN_M16_WARPS * 32) lin_mma16_kernel(const LinParams p) {
+__global__ void __launch_bounds__(LIN_M16_WARPS * 32, 3) lin_mma16_kernel(const LinParams p) {
     const int g = blockIdx.z;
     const int rows = p.cnt[(size_t)g * p.cnt_gstride];
     if (rows <= 0) return;
@@ -415,41 +415,51 @@ __global__ void __launch_bounds__(LIN_M16_WARPS * 32) lin_mma16_kernel(const Lin
         const float* xlo = rlo < rows ? X + (size_t)(p.xlist ? p.xlist[base + rlo] : base + rlo) * p.ldx : nullptr;
         const float* xhi = rhi < rows ? X + (size_t)(p.xlist ? p.xlist[base + rhi] : base + rhi) * p.ldx : nullptr;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-        for (int kb = warp * 32; kb < K; kb += LIN_M16_WARPS * 32) {
-            const int k = kb + tq * 8;
-            const int valid = max(0, min(8, K - k));
-            uint4 wq = make_uint4(0, 0, 0, 0);
-            if (nvalid && valid > 0) {
-                if (vecW) {
-                    wq = __ldg(reinterpret_cast<const uint4*>(wrow + k));
-                } else {
-                    __align__(16) __nv_bfloat16 t[8];
+        constexpr int U = 4;                       // weight loads kept in flight per lane
+        for (int kb0 = warp * 32; kb0 < K; kb0 += LIN_M16_WARPS * 32 * U) {
+            uint4 wq[U];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) t[j] = j < valid ? wrow[k + j] : __float2bfloat16(0.f);
-                    wq = *reinterpret_cast<const uint4*>(t);
+            for (int u = 0; u < U; ++u) {          // all weight loads of the batch first: they are the HBM stream
+                const int k = kb0 + u * LIN_M16_WARPS * 32 + tq * 8;
+                const int valid = max(0, min(8, K - k));
+                wq[u] = make_uint4(0, 0, 0, 0);
+                if (nvalid && valid > 0) {
+                    if (vecW) {
+                        wq[u] = __ldg(reinterpret_cast<const uint4*>(wrow + k));
+                    } else {
+                        __align__(16) __nv_bfloat16 t[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) t[j] = j < valid ? wrow[k + j] : __float2bfloat16(0.f);
+                        wq[u] = *reinterpret_cast<const uint4*>(t);
+                    }
                 }
             }
-            float lo[8], hi[8];
-            if (xlo && valid > 0) lin_ld8(xlo + k, vecX, valid, lo);
-            else {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) lo[j] = 0.f;
-            }
-            if (xhi && valid > 0) lin_ld8(xhi + k, vecX, valid, hi);
-            else {
+            for (int u = 0; u < U; ++u) {
+                const int k = kb0 + u * LIN_M16_WARPS * 32 + tq * 8;
+                const int valid = max(0, min(8, K - k));
+                if (kb0 + u * LIN_M16_WARPS * 32 >= K) break;          // warp-uniform
+                float lo[8], hi[8];
+                if (xlo && valid > 0) lin_ld8(xlo + k, vecX, valid, lo);
+                else {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) hi[j] = 0.f;
+                    for (int j = 0; j < 8; ++j) lo[j] = 0.f;
+                }
+                if (xhi && valid > 0) lin_ld8(xhi + k, vecX, valid, hi);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) hi[j] = 0.f;
+                }
+                uint32_t a[4], b[2];
+                a[0] = pack_bf16x2(make_float2(lo[0], lo[1])); a[1] = pack_bf16x2(make_float2(hi[0], hi[1]));
+                a[2] = pack_bf16x2(make_float2(lo[2], lo[3])); a[3] = pack_bf16x2(make_float2(hi[2], hi[3]));
+                b[0] = wq[u].x; b[1] = wq[u].y;
+                mma_bf16_16816(acc, a, b);
+                a[0] = pack_bf16x2(make_float2(lo[4], lo[5])); a[1] = pack_bf16x2(make_float2(hi[4], hi[5]));
+                a[2] = pack_bf16x2(make_float2(lo[6], lo[7])); a[3] = pack_bf16x2(make_float2(hi[6], hi[7]));
+                b[0] = wq[u].z; b[1] = wq[u].w;
+                mma_bf16_16816(acc, a, b);
             }
-            uint32_t a[4], b[2];
-            a[0] = pack_bf16x2(make_float2(lo[0], lo[1])); a[1] = pack_bf16x2(make_float2(hi[0], hi[1]));
-            a[2] = pack_bf16x2(make_float2(lo[2], lo[3])); a[3] = pack_bf16x2(make_float2(hi[2], hi[3]));
-            b[0] = wq.x; b[1] = wq.y;
-            mma_bf16_16816(acc, a, b);
-            a[0] = pack_bf16x2(make_float2(lo[4], lo[5])); a[1] = pack_bf16x2(make_float2(hi[4], hi[5]));
-            a[2] = pack_bf16x2(make_float2(lo[6], lo[7])); a[3] = pack_bf16x2(make_float2(hi[6], hi[7]));
-            b[0] = wq.z; b[1] = wq.w;
-            mma_bf16_16816(acc, a, b);
         }
         __syncthreads();                           // red of the previous row block has been read
         red[warp][gq][tq * 2] = acc[0]; red[warp][gq][tq * 2 + 1] = acc[1];
