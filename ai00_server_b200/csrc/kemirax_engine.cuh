@@ -273,7 +273,7 @@ void b200rwkv_engine::kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int ro
     p.max_rows = rows;
     const bool exact = kx->exact || force_exact;
     if (!exact && rows <= 16) {
-        launch_k(lin_mma16_kernel, dim3(cdiv(p.N, 8), 1, groups), dim3(LIN_M16_WARPS * 32), 0, p, KC_GEMM, s, prof);
+        launch_k(lin_mma16_kernel, dim3(cdiv(p.N, LIN_M16_BN), 1, groups), dim3(LIN_M16_WARPS * 32), 0, p, KC_GEMM, s, prof);
     } else if (rows <= LIN_SK_ROWS || (exact && rows <= 16)) {
         launch_k(lin_skinny_kernel, dim3(cdiv(p.N, 2 * LIN_SK_WARPS), 1, groups), dim3(LIN_SK_WARPS * 32), 0, p, KC_GEMM, s, prof);
     } else if (exact) {

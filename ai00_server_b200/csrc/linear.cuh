@@ -379,7 +379,7 @@ __global__ void __launch_bounds__(LIN_SK_WARPS * 32) lin_skinny_kernel(const Lin
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// steps of up to 16 rows on the tensor cores: 8 outputs per CTA, the k range split over 8 warps.  A lane streams 16 bytes of
+// steps of up to 16 rows on the tensor cores: 16 outputs per CTA, the k range split over 8 warps.  A lane streams 16 bytes of
 // one weight row (8 consecutive k) and the matching 8 activations of rows g and g + 8 straight from global memory; those 8 k
 // feed two m16n8k16 products (any fixed pairing of k between the A and B fragments is a valid sum order), so no operand
 // passes through shared memory and every weight byte is read once, in full 32-byte sectors.
@@ -396,41 +396,53 @@ __device__ __forceinline__ void lin_ld8(const float* p, bool vec, int valid, flo
     }
 }
 
+constexpr int LIN_M16_BN = 16;                     // outputs per CTA: two n8 tiles share every activation fragment
+
 __global__ void __launch_bounds__(LIN_M16_WARPS * 32, 3) lin_mma16_kernel(const LinParams p) {
     const int g = blockIdx.z;
     const int rows = p.cnt[(size_t)g * p.cnt_gstride];
     if (rows <= 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-    const int n0 = blockIdx.x * 8;
+    const int n0 = blockIdx.x * LIN_M16_BN;
     const int base = p.off ? p.off[g] : 0;
     const float* X = p.X + g * p.x_gstride;
-    const int K = p.K, n = n0 + gq;
-    const __nv_bfloat16* wrow = p.W + g * p.w_gstride + (size_t)min(n, p.N - 1) * K;
-    const bool nvalid = n < p.N;
-    const bool vecW = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.W + g * p.w_gstride) & 15) == 0);
+    const int K = p.K;
+    const __nv_bfloat16* Wg = p.W + g * p.w_gstride;
+    const __nv_bfloat16* wrow[2];
+    bool nvalid[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int n = n0 + j * 8 + gq;
+        nvalid[j] = n < p.N;
+        wrow[j] = Wg + (size_t)min(n, p.N - 1) * K;
+    }
+    const bool vecW = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(Wg) & 15) == 0);
     const bool vecX = (p.ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(X) & 15) == 0);
-    __shared__ float red[LIN_M16_WARPS][16][8];
+    __shared__ float red[LIN_M16_WARPS][16][LIN_M16_BN];
     for (int rb = 0; rb < rows; rb += 16) {
         const int rlo = rb + gq, rhi = rb + gq + 8;
         const float* xlo = rlo < rows ? X + (size_t)(p.xlist ? p.xlist[base + rlo] : base + rlo) * p.ldx : nullptr;
         const float* xhi = rhi < rows ? X + (size_t)(p.xlist ? p.xlist[base + rhi] : base + rhi) * p.ldx : nullptr;
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        constexpr int U = 4;                       // weight loads kept in flight per lane
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        constexpr int U = 2;                       // k blocks per batch: 4 weight loads in flight per lane
         for (int kb0 = warp * 32; kb0 < K; kb0 += LIN_M16_WARPS * 32 * U) {
-            uint4 wq[U];
+            uint4 wq[U][2];
 #pragma unroll
             for (int u = 0; u < U; ++u) {          // all weight loads of the batch first: they are the HBM stream
                 const int k = kb0 + u * LIN_M16_WARPS * 32 + tq * 8;
                 const int valid = max(0, min(8, K - k));
-                wq[u] = make_uint4(0, 0, 0, 0);
-                if (nvalid && valid > 0) {
-                    if (vecW) {
-                        wq[u] = __ldg(reinterpret_cast<const uint4*>(wrow + k));
-                    } else {
-                        __align__(16) __nv_bfloat16 t[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) t[j] = j < valid ? wrow[k + j] : __float2bfloat16(0.f);
-                        wq[u] = *reinterpret_cast<const uint4*>(t);
+                for (int j = 0; j < 2; ++j) {
+                    wq[u][j] = make_uint4(0, 0, 0, 0);
+                    if (nvalid[j] && valid > 0) {
+                        if (vecW) {
+                            wq[u][j] = __ldg(reinterpret_cast<const uint4*>(wrow[j] + k));
+                        } else {
+                            __align__(16) __nv_bfloat16 t[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) t[e] = e < valid ? wrow[j][k + e] : __float2bfloat16(0.f);
+                            wq[u][j] = *reinterpret_cast<const uint4*>(t);
+                        }
                     }
                 }
             }
@@ -443,30 +455,37 @@ __global__ void __launch_bounds__(LIN_M16_WARPS * 32, 3) lin_mma16_kernel(const 
                 if (xlo && valid > 0) lin_ld8(xlo + k, vecX, valid, lo);
                 else {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) lo[j] = 0.f;
+                    for (int e = 0; e < 8; ++e) lo[e] = 0.f;
                 }
                 if (xhi && valid > 0) lin_ld8(xhi + k, vecX, valid, hi);
                 else {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) hi[j] = 0.f;
+                    for (int e = 0; e < 8; ++e) hi[e] = 0.f;
                 }
-                uint32_t a[4], b[2];
-                a[0] = pack_bf16x2(make_float2(lo[0], lo[1])); a[1] = pack_bf16x2(make_float2(hi[0], hi[1]));
-                a[2] = pack_bf16x2(make_float2(lo[2], lo[3])); a[3] = pack_bf16x2(make_float2(hi[2], hi[3]));
-                b[0] = wq[u].x; b[1] = wq[u].y;
-                mma_bf16_16816(acc, a, b);
-                a[0] = pack_bf16x2(make_float2(lo[4], lo[5])); a[1] = pack_bf16x2(make_float2(hi[4], hi[5]));
-                a[2] = pack_bf16x2(make_float2(lo[6], lo[7])); a[3] = pack_bf16x2(make_float2(hi[6], hi[7]));
-                b[0] = wq[u].z; b[1] = wq[u].w;
-                mma_bf16_16816(acc, a, b);
+                uint32_t a0[4], a1[4];
+                a0[0] = pack_bf16x2(make_float2(lo[0], lo[1])); a0[1] = pack_bf16x2(make_float2(hi[0], hi[1]));
+                a0[2] = pack_bf16x2(make_float2(lo[2], lo[3])); a0[3] = pack_bf16x2(make_float2(hi[2], hi[3]));
+                a1[0] = pack_bf16x2(make_float2(lo[4], lo[5])); a1[1] = pack_bf16x2(make_float2(hi[4], hi[5]));
+                a1[2] = pack_bf16x2(make_float2(lo[6], lo[7])); a1[3] = pack_bf16x2(make_float2(hi[6], hi[7]));
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    uint32_t b[2];
+                    b[0] = wq[u][j].x; b[1] = wq[u][j].y;
+                    mma_bf16_16816(acc[j], a0, b);
+                    b[0] = wq[u][j].z; b[1] = wq[u][j].w;
+                    mma_bf16_16816(acc[j], a1, b);
+                }
             }
         }
         __syncthreads();                           // red of the previous row block has been read
-        red[warp][gq][tq * 2] = acc[0]; red[warp][gq][tq * 2 + 1] = acc[1];
-        red[warp][gq + 8][tq * 2] = acc[2]; red[warp][gq + 8][tq * 2 + 1] = acc[3];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            red[warp][gq][j * 8 + tq * 2] = acc[j][0]; red[warp][gq][j * 8 + tq * 2 + 1] = acc[j][1];
+            red[warp][gq + 8][j * 8 + tq * 2] = acc[j][2]; red[warp][gq + 8][j * 8 + tq * 2 + 1] = acc[j][3];
+        }
         __syncthreads();
-        if (threadIdx.x < 64) {
-            const int r = threadIdx.x >> 2, c = (threadIdx.x & 3) * 2;
+        if (threadIdx.x < 128) {
+            const int r = threadIdx.x >> 3, c = (threadIdx.x & 7) * 2;
             float s0 = 0.f, s1 = 0.f;
 #pragma unroll
             for (int w = 0; w < LIN_M16_WARPS; ++w) { s0 += red[w][r][c]; s1 += red[w][r][c + 1]; }
