@@ -247,6 +247,49 @@ ODD = [LA("latent_attention", heads=3, dim=12, vdim=20, rot_dim=6, kv_rank=20, q
        LA("gla", heads=1, dim=40, vdim=33, tau=1.0, experts=9, identity=1, top=4, ff=5, shared_ff=3)]
 
 
+LARGE = [LA("latent_attention", heads=20, dim=16, vdim=16, rot_dim=8, kv_rank=512, q_rank=64, experts=6, identity=2, top=4, ff=40, shared_ff=72),
+         LA("gla", heads=2, dim=64, vdim=128, mlp=False),
+         LA("latent_attention", heads=20, dim=16, vdim=16, rot_dim=8, kv_rank=512, q_rank=64, kv_from=0, mlp=False)]
+
+
+@pytest.mark.parametrize("precision", [1, 0])
+def test_largest_latent_and_many_heads(precision):
+    # the largest latent the attention kernels take (16 channel chunks per lane / 16 output tiles per warp), a head count that
+    # fills one head group and part of a second, a recurrent state of 32 KB per head
+    b = Bundle(LARGE, precision=precision, width=128, vocab=64, seed=19, gain=0.6)
+    try:
+        toks = b.tokens(44, 9)
+        want = b.oracle(toks)
+        got = np.concatenate([b.feed(0, toks[:35])] + [b.feed(0, [t], capi.OPTION_LAST) for t in toks[35:]])
+        if precision:
+            assert err(got, want) <= TIGHT
+        else:
+            assert_serving(got, want, bf16_floor(b, toks, want))
+    finally:
+        b.close()
+
+
+UNALIGNED = [LA("latent_attention", heads=2, dim=5, vdim=3, rot_dim=2, kv_rank=10, q_rank=7, experts=2, identity=1, top=2, ff=3, shared_ff=5),
+             LA("gla", heads=3, dim=5, vdim=3, experts=3, identity=0, top=1, ff=9, shared_ff=0),
+             LA("latent_attention", heads=2, dim=5, vdim=3, rot_dim=2, kv_rank=10, q_rank=7, kv_from=0, mlp=False)]
+
+
+@pytest.mark.parametrize("precision", [1, 0])
+def test_sizes_that_align_with_nothing(precision):
+    # width, ranks and vocabulary that are no multiple of 4 or 8: every vector path has to fall back to its scalar form
+    b = Bundle(UNALIGNED, precision=precision, width=50, vocab=37, seed=17, a_rank=3)
+    try:
+        toks = b.tokens(41, 8)
+        want = b.oracle(toks)
+        got = np.concatenate([b.feed(0, toks[:18])] + [b.feed(0, [t], capi.OPTION_LAST) for t in toks[18:24]] + [b.feed(0, toks[24:])])
+        if precision:
+            assert err(got, want) <= TIGHT
+        else:
+            assert_serving(got, want, bf16_floor(b, toks, want))
+    finally:
+        b.close()
+
+
 @pytest.mark.parametrize("precision", [1, 0])
 def test_other_sizes(precision):
     b = Bundle(ODD, precision=precision, width=72, vocab=101, seed=11, a_rank=5, eps=1e-3)
