@@ -42,7 +42,8 @@ class Options(C.Structure):
 
 
 QUANT_NONE, QUANT_INT8, QUANT_NF4 = 0, 1, 2
-ARCH_KEMIRAX = 100          # Info.version of the config.json-described family
+ARCH_KEMIRAX = 100          # Info.version of the config.json-described families
+ARCH_DEGAVIK = 101
 
 
 class B200Error(RuntimeError):

@@ -35,6 +35,9 @@
 #include "latent_attn.cuh"
 #include "gla.cuh"
 #include "moe.cuh"
+#include "retention.cuh"
+#include "delta_rule.cuh"
+#include "window_attn.cuh"
 
 namespace b200 {
 
@@ -284,12 +287,19 @@ private:
 static b200rwkv_info derive_info(const StFile& st) {
     b200rwkv_info o;
     memset(&o, 0, sizeof(o));
-    if (st.find("embed") && st.find("l0.norm1") && st.find("final.norm")) {      // Kemirax family: sizes of its layers are in config.json
+    if (st.find("embed") && st.find("final.norm")) {      // families whose layer sizes are in a config.json
         const StTensor& e = *st.find("embed");
-        o.version = B200RWKV_ARCH_KEMIRAX;
+        // Kemirax norms are one gain; Degavik norms are weight vectors (and a layer may have no tensors of its own)
+        o.version = st.find("final.norm")->numel() == 1 ? B200RWKV_ARCH_KEMIRAX : B200RWKV_ARCH_DEGAVIK;
         o.num_vocab = (int)StFile::dim(e, 0, "embed", 2);
         o.num_emb = (int)StFile::dim(e, 1, "embed", 2);
-        while (st.find("l" + std::to_string(o.num_layer) + ".norm1")) ++o.num_layer;
+        if (o.version == B200RWKV_ARCH_KEMIRAX) {
+            while (st.find("l" + std::to_string(o.num_layer) + ".norm1")) ++o.num_layer;
+        } else {                                           // layers that own tensors (the config lists the rest)
+            for (int i = 0, miss = 0; miss < 64; ++i) {
+                if (st.find("l" + std::to_string(i) + ".norm1")) { o.num_layer = i + 1; miss = 0; } else ++miss;
+            }
+        }
         return o;
     }
     o.num_vocab = (int)st.dim("emb.weight", 0, 2);
@@ -402,6 +412,7 @@ struct Snapshot { float* buf = nullptr; float* logits = nullptr; size_t bytes = 
 }  // namespace b200
 
 #include "kemirax.cuh"
+#include "degavik.cuh"
 
 using namespace b200;
 
@@ -508,6 +519,11 @@ struct b200rwkv_engine {
     std::unique_ptr<Kemirax> kx;
     int kv_tokens = 0, kv_page = 0;               // attention cache capacity (tokens over all live sequences) and page size
     void kx_build(const StFile& st, const char* cfg_json, size_t cfg_len);
+    void kx_load(const StFile& st, KxSizes& z);
+    void dg_load(const StFile& st, KxSizes& z);                   // Degavik family (degavik_engine.cuh)
+    void dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int nslot_grid, bool decode, Profiler* prof);
+    __nv_bfloat16* kx_up16(const std::vector<uint16_t>& v);
+    float* kx_up32(const std::vector<float>& v);
     void kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int rows, int groups, bool force_exact = false);
     void kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool decode, int nsplit, Profiler* prof);
     void kx_fill_step(int* hm, const std::vector<int>& slots, const std::vector<int>& counts, bool* decode, int* nsplit);
@@ -1812,6 +1828,7 @@ void b200rwkv_engine::state_xform(int slot, bool import, float* snap) {
 }
 
 #include "kemirax_engine.cuh"
+#include "degavik_engine.cuh"
 
 // =========================================================================================
 // in-process tensor-parallel group
@@ -1974,7 +1991,7 @@ static int32_t create_rank(const uint8_t* st, size_t len, int32_t device, int32_
     if (config_json && config_len > 0) {
         e->kx_build(f, config_json, config_len);
     } else {
-        REQUIRE(derive_info(f).version != B200RWKV_ARCH_KEMIRAX, B200RWKV_ERR_INVALID, "this model needs its config.json (b200rwkv_options.config_json)");
+        REQUIRE(derive_info(f).version < B200RWKV_ARCH_KEMIRAX, B200RWKV_ERR_INVALID, "this model needs its config.json (b200rwkv_options.config_json)");
         e->build(f);
     }
     e->loras.clear();            // the LoRA images are only borrowed during the build

@@ -106,11 +106,20 @@ private:
 // ------------------------------------------------------------------------------------------------------------------
 struct RotCfg { int dims = 0; double base = 10000.0; bool scaled = false; double factor = 1, original = 0, fast = 0, slow = 0; };
 
-enum KxMixer { KX_LATENT = 0, KX_GLA = 1 };
+enum KxMixer { KX_LATENT = 0, KX_GLA = 1, KX_RETENTION = 2, KX_DELTA = 3, KX_WINDOW = 4 };
+enum KxFamily { KX_FAMILY_KEMIRAX = 0, KX_FAMILY_DEGAVIK = 1 };
 
 struct KxLayerCfg {
     int mixer = KX_LATENT;
     int heads = 0, dim = 0, vdim = 0;
+    // Degavik mixers (degavik.cuh)
+    int kv_heads = 0;                                            // delta rule, windowed attention
+    int taps = 0;                                                // delta rule: short convolution length
+    int window = 0, keep_first = 0;                              // windowed attention
+    float softcap = 0.f;
+    std::vector<double> decay;                                   // retention: one per head
+    int weights_of = -1;                                         // the layer whose tensors this layer uses (-1: its own)
+    bool mlp_dense = false;                                      // feed-forward is one gated unit, not routed experts
     int rot_dim = 0, kv_rank = 0, q_rank = 0, kv_from = -1;     // latent attention
     float scale = 1.f;
     RotCfg rot;
@@ -124,15 +133,22 @@ struct KxLayerCfg {
 };
 
 struct KxConfig {
+    int family = KX_FAMILY_KEMIRAX;
     int vocab = 0, width = 0;
     float eps = 1e-5f;
     std::vector<KxLayerCfg> layers;
 };
 
+static KxConfig dg_parse_config(const JVal& root);
+
+// model registry of the families that come with a config.json: `architecture` names the design
 static KxConfig kx_parse_config(const char* json, size_t n) {
     JVal root = JsonParser(json, n).parse();
     REQUIRE(root.kind == JVal::OBJ, B200RWKV_ERR_INVALID, "config: not an object");
-    REQUIRE(root.has("architecture") && root.at("architecture").str == "Kemirax", B200RWKV_ERR_UNSUPPORTED, "config: architecture is not Kemirax");
+    REQUIRE(root.has("architecture") && root.at("architecture").kind == JVal::STR, B200RWKV_ERR_INVALID, "config: no architecture");
+    const std::string arch = root.at("architecture").str;
+    if (arch == "Degavik") return dg_parse_config(root);
+    REQUIRE(arch == "Kemirax", B200RWKV_ERR_UNSUPPORTED, "config: unknown architecture '" + arch + "'");
     KxConfig c;
     c.vocab = root.integer("vocab");
     c.width = root.integer("width");
@@ -224,6 +240,25 @@ struct KxLayer {
     // feed-forward
     __nv_bfloat16 *router = nullptr, *gu = nullptr, *down = nullptr, *sh_gu = nullptr, *sh_down = nullptr, *sg = nullptr;
     float* corr = nullptr;
+    // Degavik: norms on the sublayers' outputs, retention / delta-rule / windowed-attention mixers
+    float *norm1_w = nullptr, *norm2_w = nullptr;
+    float *decay = nullptr;                                      // retention [H]
+    __nv_bfloat16 *g2 = nullptr;                                 // delta rule: output-gate up-projection (a2 = decay up-projection)
+    float *a_log = nullptr, *conv_w = nullptr, *conv_tail = nullptr;   // delta rule: [H], [C][taps], [S][taps - 1][C]
+    int g_rank = 0, conv_C = 0;
+    float *qn_w = nullptr, *kn_w = nullptr, *talk = nullptr, *temp = nullptr;   // windowed attention
+    float* rec_state = nullptr;                                  // retention / delta rule: [S][H][dk][dv]
+    int cache_D = 0;                                             // floats per cached token when the layer owns a pool
+    // per-sequence memory of fixed size, in the order of the flat state record
+    struct Block { float* base; size_t per_slot; };
+    std::vector<Block> fixed;
+};
+
+// largest per-token widths of the activation buffers over the layers of a model (filled by the family's loader)
+struct KxSizes {
+    size_t n_cq = 1, n_q = 1, n_qa = 1, n_kv = 1, n_part = 1, n_olat = 1, n_vout = 1, n_pr = 1, n_z = 1, n_rl = 1, n_yc = 1, n_ys = 1,
+           n_cv = 1, n_gl = 1, n_bl = 1;
+    int max_top = 1, max_E = 1;
 };
 
 struct Kemirax {
@@ -232,6 +267,9 @@ struct Kemirax {
     bool exact = false;
     int W = 0, V = 0, page = 64, npages = 0, state_ctx = 0;
     float final_gain = 1.f;
+    float* final_w = nullptr;                     // weight vector of the last norm (families that have one)
+    int qb_prompt = 4;                            // tokens per attention chunk of a prompt step
+    float *y = nullptr, *cv = nullptr, *gl = nullptr, *bl = nullptr;   // sublayer output, convolution output, gate / strength logits
     __nv_bfloat16 *embed = nullptr, *head = nullptr;
     // sequence memory
     int* d_table = nullptr;                       // [S][npages]

@@ -4,6 +4,17 @@
 
 namespace b200 {
 
+static void kx_cat(std::vector<uint16_t>& a, const std::vector<uint16_t>& b) { a.insert(a.end(), b.begin(), b.end()); }
+// (gate, up) -> rows interleaved so that outputs (2i, 2i+1) are one gated unit
+static std::vector<uint16_t> kx_interleave(const std::vector<uint16_t>& gt, const std::vector<uint16_t>& upw, int ff, int K) {
+    std::vector<uint16_t> o((size_t)2 * ff * K);
+    for (int i = 0; i < ff; ++i) {
+        memcpy(&o[(size_t)(2 * i) * K], &gt[(size_t)i * K], (size_t)K * 2);
+        memcpy(&o[(size_t)(2 * i + 1) * K], &upw[(size_t)i * K], (size_t)K * 2);
+    }
+    return o;
+}
+
 static std::vector<uint16_t> kx_host_bf16(const StFile& st, const std::string& name, int64_t rows, int64_t cols) {
     const StTensor* t = st.find(name);
     REQUIRE(t, B200RWKV_ERR_INVALID, "missing tensor: " + name);
@@ -35,14 +46,142 @@ static std::vector<float> kx_host_f32(const StFile& st, const std::string& name,
 
 using namespace b200;
 
+__nv_bfloat16* b200rwkv_engine::kx_up16(const std::vector<uint16_t>& v) {
+    __nv_bfloat16* d = (__nv_bfloat16*)dalloc(std::max<size_t>(v.size(), 1) * 2, false);
+    if (!v.empty()) CK(cudaMemcpy(d, v.data(), v.size() * 2, cudaMemcpyHostToDevice));
+    weight_bytes_total += v.size() * 2;
+    return d;
+}
+float* b200rwkv_engine::kx_up32(const std::vector<float>& v) {
+    float* d = (float*)dalloc(std::max<size_t>(v.size(), 1) * 4, false);
+    if (!v.empty()) CK(cudaMemcpy(d, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
+    return d;
+}
+
 size_t Kemirax::flat_floats(int ctx_rows) const {
     size_t n = 4;                                          // [0] tokens held
     for (const KxLayer& l : layers) {
-        n += (size_t)W;
-        if (l.c.mixer == KX_GLA) n += (size_t)l.c.heads * l.c.dim * l.c.vdim;
-        else if (l.c.kv_from < 0) n += (size_t)ctx_rows * (l.c.kv_rank + l.c.rot_dim);
+        for (const KxLayer::Block& b : l.fixed) n += b.per_slot;
+        n += (size_t)ctx_rows * l.cache_D;
     }
     return n;
+}
+
+// tensors of a Kemirax model -> device, stacked / interleaved / transposed as the grouped launches want them
+void b200rwkv_engine::kx_load(const StFile& st, KxSizes& z) {
+    Kemirax& m = *kx;
+    const int W = m.W, nl = (int)m.cfg.layers.size();
+    m.embed = kx_up16(kx_host_bf16(st, "embed", m.V, W));
+    m.head = kx_up16(kx_host_bf16(st, "head", m.V, W));
+    m.final_gain = kx_host_f32(st, "final.norm", 1)[0];
+    emb = nullptr;
+
+    m.layers.resize(nl);
+    for (int i = 0; i < nl; ++i) {
+        KxLayer& l = m.layers[i];
+        l.c = m.cfg.layers[i];
+        const KxLayerCfg& c = l.c;
+        const std::string p = "l" + std::to_string(i) + ".";
+        l.gain = kx_host_f32(st, p + "norm1", 1)[0];
+        l.mu = kx_up32(kx_host_f32(st, p + "shift", W));
+        l.shift_state = (float*)dalloc((size_t)S * W * 4);
+        l.fixed.push_back({l.shift_state, (size_t)W});
+        {
+            auto g = kx_host_bf16(st, p + "rg1", W, W);
+            auto b = kx_host_f32(st, p + "rg1.b", W);
+            if (c.has_mlp) {
+                kx_cat(g, kx_host_bf16(st, p + "rg2", W, W));
+                auto b2 = kx_host_f32(st, p + "rg2.b", W);
+                b.insert(b.end(), b2.begin(), b2.end());
+            }
+            l.rg = kx_up16(g); l.rg_b = kx_up32(b);
+        }
+        REQUIRE(c.heads >= 1 && c.dim >= 1 && c.vdim >= 1, B200RWKV_ERR_INVALID, "config: bad mixer sizes");
+        if (c.mixer == KX_LATENT) {
+            const int H_ = c.heads, dn = c.dim, dr = c.rot_dim, dv = c.vdim, rk = c.kv_rank, D = rk + dr;
+            REQUIRE(rk >= 1 && rk <= 32 * LA_MAX_RK_CHUNKS, B200RWKV_ERR_UNSUPPORTED, "kv_rank must be in 1..512");
+            REQUIRE(c.rot.dims % 2 == 0 && c.rot.dims <= dr, B200RWKV_ERR_INVALID, "config: rot.dims must be even and <= rot_dim");
+            REQUIRE((latent_attn_smem<1, 16>(D)) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "kv_rank + rot_dim too large for the attention tile");
+            l.dq = kx_up16(kx_host_bf16(st, p + "mix.dq", c.q_rank, W));
+            l.dq_norm = kx_up32(kx_host_f32(st, p + "mix.dq.norm", c.q_rank));
+            l.uq = kx_up16(kx_host_bf16(st, p + "mix.uq", (int64_t)H_ * (dn + dr), c.q_rank));
+            {   // W_uk [H * dn, rk] -> per head transposed [rk, dn]: qa[h] = W_uk[h]^T q_plain[h] becomes a linear
+                auto uk = kx_host_bf16(st, p + "mix.uk", (int64_t)H_ * dn, rk);
+                std::vector<uint16_t> t(uk.size());
+                for (int hh = 0; hh < H_; ++hh)
+                    for (int d = 0; d < dn; ++d)
+                        for (int r = 0; r < rk; ++r) t[((size_t)hh * rk + r) * dn + d] = uk[((size_t)hh * dn + d) * rk + r];
+                l.ukT = kx_up16(t);
+            }
+            l.uv = kx_up16(kx_host_bf16(st, p + "mix.uv", (int64_t)H_ * dv, rk));
+            l.o = kx_up16(kx_host_bf16(st, p + "mix.o", W, (int64_t)H_ * dv));
+            std::vector<float> fr;
+            kx_rot_table(c.rot, fr, l.mag);
+            l.freq = kx_up32(fr);
+            if (c.kv_from < 0) {
+                l.dkv = kx_up16(kx_host_bf16(st, p + "mix.dkv", D, W));
+                l.dkv_norm = kx_up32(kx_host_f32(st, p + "mix.dkv.norm", rk));
+                l.cache = (float*)dalloc((size_t)m.npages * m.page * D * 4);
+                l.cache_D = D;
+            } else {
+                REQUIRE(c.kv_from < i, B200RWKV_ERR_INVALID, "config: kv_from must name an earlier layer");
+                const KxLayer& src = m.layers[c.kv_from];
+                REQUIRE(src.c.mixer == KX_LATENT && src.c.kv_from < 0 && src.c.kv_rank == rk && src.c.rot_dim == dr, B200RWKV_ERR_INVALID,
+                        "config: kv_from must name a latent-attention layer with its own cache of the same shape");
+                l.cache = src.cache;
+            }
+            z.n_cq = std::max(z.n_cq, (size_t)c.q_rank); z.n_q = std::max(z.n_q, (size_t)H_ * (dn + dr)); z.n_qa = std::max(z.n_qa, (size_t)H_ * D);
+            z.n_kv = std::max(z.n_kv, (size_t)D); z.n_part = std::max(z.n_part, (size_t)H_ * m.max_split * (rk + 2));
+            z.n_olat = std::max(z.n_olat, (size_t)H_ * rk); z.n_vout = std::max(z.n_vout, (size_t)H_ * dv);
+            m.max_D = std::max(m.max_D, D);
+        } else {
+            const int H_ = c.heads, dk = c.dim, dv = c.vdim;
+            REQUIRE(dv <= 1024, B200RWKV_ERR_UNSUPPORTED, "gla vdim must be <= 1024");
+            REQUIRE(gla_smem_bytes(dk, dv) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "gla head state too large for shared memory");
+            const StTensor* a1 = st.find(p + "mix.a1");
+            REQUIRE(a1 && a1->shape.size() == 2, B200RWKV_ERR_INVALID, "missing tensor: " + p + "mix.a1");
+            l.a_rank = (int)a1->shape[0];
+            auto w = kx_host_bf16(st, p + "mix.q", (int64_t)H_ * dk, W);
+            kx_cat(w, kx_host_bf16(st, p + "mix.k", (int64_t)H_ * dk, W));
+            kx_cat(w, kx_host_bf16(st, p + "mix.v", (int64_t)H_ * dv, W));
+            kx_cat(w, kx_host_bf16(st, p + "mix.g", (int64_t)H_ * dv, W));
+            kx_cat(w, kx_host_bf16(st, p + "mix.a1", l.a_rank, W));
+            l.proj_n = 2 * H_ * dk + 2 * H_ * dv + l.a_rank;
+            l.proj = kx_up16(w);
+            l.a2 = kx_up16(kx_host_bf16(st, p + "mix.a2", (int64_t)H_ * dk, l.a_rank));
+            l.a2_b = kx_up32(kx_host_f32(st, p + "mix.a2.b", (int64_t)H_ * dk));
+            l.norm_w = kx_up32(kx_host_f32(st, p + "mix.norm", dv));
+            l.o = kx_up16(kx_host_bf16(st, p + "mix.o", W, (int64_t)H_ * dv));
+            l.gla_state = (float*)dalloc((size_t)S * H_ * dk * dv * 4);
+            l.fixed.push_back({l.gla_state, (size_t)H_ * dk * dv});
+            z.n_pr = std::max(z.n_pr, (size_t)l.proj_n); z.n_z = std::max(z.n_z, (size_t)H_ * dk); z.n_vout = std::max(z.n_vout, (size_t)H_ * dv);
+        }
+        if (c.has_mlp) {
+            const int E = c.experts, NE = E + c.identity, ff = c.ff;
+            REQUIRE(c.top >= 1 && c.top <= MOE_MAX_TOP && c.top <= NE && E >= 0 && NE >= 1 && NE <= 2048, B200RWKV_ERR_UNSUPPORTED,
+                    "config: router sizes out of range (top <= 8, outputs <= 2048)");
+            l.router = kx_up16(kx_host_bf16(st, p + "mlp.router", NE, W));
+            if (st.find(p + "mlp.correction")) l.corr = kx_up32(kx_host_f32(st, p + "mlp.correction", NE));
+            if (E > 0) {
+                std::vector<uint16_t> gu, dw;
+                for (int e = 0; e < E; ++e) {
+                    const std::string q = p + "mlp.e" + std::to_string(e) + ".";
+                    kx_cat(gu, kx_interleave(kx_host_bf16(st, q + "gate", ff, W), kx_host_bf16(st, q + "up", ff, W), ff, W));
+                    kx_cat(dw, kx_host_bf16(st, q + "down", W, ff));
+                }
+                l.gu = kx_up16(gu); l.down = kx_up16(dw);
+            }
+            if (c.has_shared) {
+                l.sh_gu = kx_up16(kx_interleave(kx_host_bf16(st, p + "mlp.shared.gate", c.sff, W), kx_host_bf16(st, p + "mlp.shared.up", c.sff, W), c.sff, W));
+                l.sh_down = kx_up16(kx_host_bf16(st, p + "mlp.shared.down", W, c.sff));
+                l.sg = kx_up16(kx_host_bf16(st, p + "mlp.shared.sg", 1, W));
+                z.n_ys = std::max(z.n_ys, (size_t)c.sff);
+            }
+            z.n_rl = std::max(z.n_rl, (size_t)NE); z.n_yc = std::max(z.n_yc, (size_t)ff);
+            z.max_top = std::max(z.max_top, c.top); z.max_E = std::max(z.max_E, std::max(E, 1));
+        }
+    }
+
 }
 
 void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cfg_len) {
@@ -53,10 +192,10 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
     m.W = m.cfg.width; m.V = m.cfg.vocab;
     const int W = m.W, nl = (int)m.cfg.layers.size();
     memset(&info, 0, sizeof(info));
-    info.version = B200RWKV_ARCH_KEMIRAX; info.num_layer = nl; info.num_emb = W; info.num_vocab = m.V;
+    info.version = m.cfg.family == KX_FAMILY_DEGAVIK ? B200RWKV_ARCH_DEGAVIK : B200RWKV_ARCH_KEMIRAX; info.num_layer = nl; info.num_emb = W; info.num_vocab = m.V;
     L = nl; C = W; V = m.V; Vl = V; Cl = C; H = Hl = 0; N = 0; F = Fl = 0;
-    REQUIRE(world == 1, B200RWKV_ERR_UNSUPPORTED, "Kemirax models run on one GPU in this version");
-    REQUIRE(quant_layers == 0 && loras.empty(), B200RWKV_ERR_UNSUPPORTED, "Kemirax models take no LoRA / quantised layers");
+    REQUIRE(world == 1, B200RWKV_ERR_UNSUPPORTED, "models that come with a config.json run on one GPU in this version");
+    REQUIRE(quant_layers == 0 && loras.empty(), B200RWKV_ERR_UNSUPPORTED, "models that come with a config.json take no LoRA / quantised layers");
     use_pdl = false;                                       // these kernels carry no programmatic-dependency waits
     // steps of up to 512 tokens when the caller's token_chunk_size asks for them (prompts then stream the weights once per 512
     // tokens and fill the experts' row tiles); 128 otherwise, like the other families
@@ -85,150 +224,24 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
     m.pages.assign(S, {});
     for (int i = m.npages - 1; i >= 0; --i) m.free_pages.push_back(i);
 
-    auto up16 = [&](const std::vector<uint16_t>& v) {
-        __nv_bfloat16* d = (__nv_bfloat16*)dalloc(v.size() * 2, false);
-        CK(cudaMemcpy(d, v.data(), v.size() * 2, cudaMemcpyHostToDevice));
-        weight_bytes_total += v.size() * 2;
-        return d;
-    };
-    auto up32 = [&](const std::vector<float>& v) {
-        float* d = (float*)dalloc(v.size() * 4, false);
-        CK(cudaMemcpy(d, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
-        return d;
-    };
-    auto cat = [](std::vector<uint16_t>& a, const std::vector<uint16_t>& b) { a.insert(a.end(), b.begin(), b.end()); };
-    // (gate, up) -> rows interleaved so that outputs (2i, 2i+1) are one gated unit
-    auto interleave = [&](const std::vector<uint16_t>& gt, const std::vector<uint16_t>& upw, int ff, int K) {
-        std::vector<uint16_t> o((size_t)2 * ff * K);
-        for (int i = 0; i < ff; ++i) {
-            memcpy(&o[(size_t)(2 * i) * K], &gt[(size_t)i * K], (size_t)K * 2);
-            memcpy(&o[(size_t)(2 * i + 1) * K], &upw[(size_t)i * K], (size_t)K * 2);
-        }
-        return o;
-    };
-
-    m.embed = up16(kx_host_bf16(st, "embed", m.V, W));
-    m.head = up16(kx_host_bf16(st, "head", m.V, W));
-    m.final_gain = kx_host_f32(st, "final.norm", 1)[0];
+    KxSizes z;
+    if (m.cfg.family == KX_FAMILY_DEGAVIK) dg_load(st, z);
+    else kx_load(st, z);
     emb = nullptr;
-
-    size_t n_cq = 1, n_q = 1, n_qa = 1, n_kv = 1, n_part = 1, n_olat = 1, n_vout = 1, n_pr = 1, n_z = 1, n_rl = 1, n_yc = 1, n_ys = 1;
-    int max_top = 1, max_E = 1;
-    m.layers.resize(nl);
-    for (int i = 0; i < nl; ++i) {
-        KxLayer& l = m.layers[i];
-        l.c = m.cfg.layers[i];
-        const KxLayerCfg& c = l.c;
-        const std::string p = "l" + std::to_string(i) + ".";
-        l.gain = kx_host_f32(st, p + "norm1", 1)[0];
-        l.mu = up32(kx_host_f32(st, p + "shift", W));
-        l.shift_state = (float*)dalloc((size_t)S * W * 4);
-        {
-            auto g = kx_host_bf16(st, p + "rg1", W, W);
-            auto b = kx_host_f32(st, p + "rg1.b", W);
-            if (c.has_mlp) {
-                cat(g, kx_host_bf16(st, p + "rg2", W, W));
-                auto b2 = kx_host_f32(st, p + "rg2.b", W);
-                b.insert(b.end(), b2.begin(), b2.end());
-            }
-            l.rg = up16(g); l.rg_b = up32(b);
-        }
-        REQUIRE(c.heads >= 1 && c.dim >= 1 && c.vdim >= 1, B200RWKV_ERR_INVALID, "config: bad mixer sizes");
-        if (c.mixer == KX_LATENT) {
-            const int H_ = c.heads, dn = c.dim, dr = c.rot_dim, dv = c.vdim, rk = c.kv_rank, D = rk + dr;
-            REQUIRE(rk >= 1 && rk <= 32 * LA_MAX_RK_CHUNKS, B200RWKV_ERR_UNSUPPORTED, "kv_rank must be in 1..512");
-            REQUIRE(c.rot.dims % 2 == 0 && c.rot.dims <= dr, B200RWKV_ERR_INVALID, "config: rot.dims must be even and <= rot_dim");
-            REQUIRE((latent_attn_smem<1, 16>(D)) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "kv_rank + rot_dim too large for the attention tile");
-            l.dq = up16(kx_host_bf16(st, p + "mix.dq", c.q_rank, W));
-            l.dq_norm = up32(kx_host_f32(st, p + "mix.dq.norm", c.q_rank));
-            l.uq = up16(kx_host_bf16(st, p + "mix.uq", (int64_t)H_ * (dn + dr), c.q_rank));
-            {   // W_uk [H * dn, rk] -> per head transposed [rk, dn]: qa[h] = W_uk[h]^T q_plain[h] becomes a linear
-                auto uk = kx_host_bf16(st, p + "mix.uk", (int64_t)H_ * dn, rk);
-                std::vector<uint16_t> t(uk.size());
-                for (int hh = 0; hh < H_; ++hh)
-                    for (int d = 0; d < dn; ++d)
-                        for (int r = 0; r < rk; ++r) t[((size_t)hh * rk + r) * dn + d] = uk[((size_t)hh * dn + d) * rk + r];
-                l.ukT = up16(t);
-            }
-            l.uv = up16(kx_host_bf16(st, p + "mix.uv", (int64_t)H_ * dv, rk));
-            l.o = up16(kx_host_bf16(st, p + "mix.o", W, (int64_t)H_ * dv));
-            std::vector<float> fr;
-            kx_rot_table(c.rot, fr, l.mag);
-            l.freq = up32(fr);
-            if (c.kv_from < 0) {
-                l.dkv = up16(kx_host_bf16(st, p + "mix.dkv", D, W));
-                l.dkv_norm = up32(kx_host_f32(st, p + "mix.dkv.norm", rk));
-                l.cache = (float*)dalloc((size_t)m.npages * m.page * D * 4);
-            } else {
-                REQUIRE(c.kv_from < i, B200RWKV_ERR_INVALID, "config: kv_from must name an earlier layer");
-                const KxLayer& src = m.layers[c.kv_from];
-                REQUIRE(src.c.mixer == KX_LATENT && src.c.kv_from < 0 && src.c.kv_rank == rk && src.c.rot_dim == dr, B200RWKV_ERR_INVALID,
-                        "config: kv_from must name a latent-attention layer with its own cache of the same shape");
-                l.cache = src.cache;
-            }
-            n_cq = std::max(n_cq, (size_t)c.q_rank); n_q = std::max(n_q, (size_t)H_ * (dn + dr)); n_qa = std::max(n_qa, (size_t)H_ * D);
-            n_kv = std::max(n_kv, (size_t)D); n_part = std::max(n_part, (size_t)H_ * m.max_split * (rk + 2));
-            n_olat = std::max(n_olat, (size_t)H_ * rk); n_vout = std::max(n_vout, (size_t)H_ * dv);
-            m.max_D = std::max(m.max_D, D);
-        } else {
-            const int H_ = c.heads, dk = c.dim, dv = c.vdim;
-            REQUIRE(dv <= 1024, B200RWKV_ERR_UNSUPPORTED, "gla vdim must be <= 1024");
-            REQUIRE(gla_smem_bytes(dk, dv) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "gla head state too large for shared memory");
-            const StTensor* a1 = st.find(p + "mix.a1");
-            REQUIRE(a1 && a1->shape.size() == 2, B200RWKV_ERR_INVALID, "missing tensor: " + p + "mix.a1");
-            l.a_rank = (int)a1->shape[0];
-            auto w = kx_host_bf16(st, p + "mix.q", (int64_t)H_ * dk, W);
-            cat(w, kx_host_bf16(st, p + "mix.k", (int64_t)H_ * dk, W));
-            cat(w, kx_host_bf16(st, p + "mix.v", (int64_t)H_ * dv, W));
-            cat(w, kx_host_bf16(st, p + "mix.g", (int64_t)H_ * dv, W));
-            cat(w, kx_host_bf16(st, p + "mix.a1", l.a_rank, W));
-            l.proj_n = 2 * H_ * dk + 2 * H_ * dv + l.a_rank;
-            l.proj = up16(w);
-            l.a2 = up16(kx_host_bf16(st, p + "mix.a2", (int64_t)H_ * dk, l.a_rank));
-            l.a2_b = up32(kx_host_f32(st, p + "mix.a2.b", (int64_t)H_ * dk));
-            l.norm_w = up32(kx_host_f32(st, p + "mix.norm", dv));
-            l.o = up16(kx_host_bf16(st, p + "mix.o", W, (int64_t)H_ * dv));
-            l.gla_state = (float*)dalloc((size_t)S * H_ * dk * dv * 4);
-            n_pr = std::max(n_pr, (size_t)l.proj_n); n_z = std::max(n_z, (size_t)H_ * dk); n_vout = std::max(n_vout, (size_t)H_ * dv);
-        }
-        if (c.has_mlp) {
-            const int E = c.experts, NE = E + c.identity, ff = c.ff;
-            REQUIRE(c.top >= 1 && c.top <= MOE_MAX_TOP && c.top <= NE && E >= 0 && NE >= 1 && NE <= 2048, B200RWKV_ERR_UNSUPPORTED,
-                    "config: router sizes out of range (top <= 8, outputs <= 2048)");
-            l.router = up16(kx_host_bf16(st, p + "mlp.router", NE, W));
-            if (st.find(p + "mlp.correction")) l.corr = up32(kx_host_f32(st, p + "mlp.correction", NE));
-            if (E > 0) {
-                std::vector<uint16_t> gu, dw;
-                for (int e = 0; e < E; ++e) {
-                    const std::string q = p + "mlp.e" + std::to_string(e) + ".";
-                    cat(gu, interleave(kx_host_bf16(st, q + "gate", ff, W), kx_host_bf16(st, q + "up", ff, W), ff, W));
-                    cat(dw, kx_host_bf16(st, q + "down", W, ff));
-                }
-                l.gu = up16(gu); l.down = up16(dw);
-            }
-            if (c.has_shared) {
-                l.sh_gu = up16(interleave(kx_host_bf16(st, p + "mlp.shared.gate", c.sff, W), kx_host_bf16(st, p + "mlp.shared.up", c.sff, W), c.sff, W));
-                l.sh_down = up16(kx_host_bf16(st, p + "mlp.shared.down", W, c.sff));
-                l.sg = up16(kx_host_bf16(st, p + "mlp.shared.sg", 1, W));
-                n_ys = std::max(n_ys, (size_t)c.sff);
-            }
-            n_rl = std::max(n_rl, (size_t)NE); n_yc = std::max(n_yc, (size_t)ff);
-            max_top = std::max(max_top, c.top); max_E = std::max(max_E, std::max(E, 1));
-        }
-    }
 
     // ---- activations (maxT rows each) ----
     const size_t T_ = (size_t)maxT;
     auto fa = [&](size_t n) { return (float*)dalloc(n * 4); };
     m.x = fa(T_ * W); m.h = fa(T_ * W); m.hs = fa(T_ * W); m.G = fa(T_ * 2 * W); m.hn = fa(T_ * W);
-    m.cq = fa(T_ * n_cq); m.q = fa(T_ * n_q); m.qa = fa(T_ * n_qa); m.kv = fa(T_ * n_kv); m.part = fa(T_ * n_part);
-    m.olat = fa(T_ * n_olat); m.vout = fa(T_ * n_vout); m.pr = fa(T_ * n_pr); m.z = fa(T_ * n_z);
-    m.rl = fa(T_ * n_rl); m.wgt = fa(T_ * max_top); m.yc = fa(T_ * max_top * n_yc); m.dn = fa(T_ * max_top * W);
-    m.ys = fa(T_ * n_ys); m.ds = fa(T_ * W);
+    m.cq = fa(T_ * z.n_cq); m.q = fa(T_ * z.n_q); m.qa = fa(T_ * z.n_qa); m.kv = fa(T_ * z.n_kv); m.part = fa(T_ * z.n_part);
+    m.olat = fa(T_ * z.n_olat); m.vout = fa(T_ * z.n_vout); m.pr = fa(T_ * z.n_pr); m.z = fa(T_ * z.n_z);
+    m.rl = fa(T_ * z.n_rl); m.wgt = fa(T_ * z.max_top); m.yc = fa(T_ * z.max_top * z.n_yc); m.dn = fa(T_ * z.max_top * W);
+    m.ys = fa(T_ * z.n_ys); m.ds = fa(T_ * W);
+    m.y = fa(T_ * W); m.cv = fa(T_ * z.n_cv); m.gl = fa(T_ * z.n_gl); m.bl = fa(T_ * z.n_bl);
     m.lin_ws_floats = (size_t)4 << 20;                   // split-k partial sums of one projection launch
     m.lin_ws = fa(m.lin_ws_floats);
-    m.sel = (int*)dalloc(T_ * max_top * 4); m.row_of = (int*)dalloc(T_ * max_top * 4); m.list = (int*)dalloc(T_ * max_top * 4);
-    m.cnt = (int*)dalloc((size_t)max_E * 4); m.off = (int*)dalloc((size_t)max_E * 4);
+    m.sel = (int*)dalloc(T_ * z.max_top * 4); m.row_of = (int*)dalloc(T_ * z.max_top * 4); m.list = (int*)dalloc(T_ * z.max_top * 4);
+    m.cnt = (int*)dalloc((size_t)z.max_E * 4); m.off = (int*)dalloc((size_t)z.max_E * 4);
     d_hidden = fa(T_ * W);
     d_logits = fa(T_ * V);
     d_api = fa(m.flat_floats(m.state_ctx));
@@ -313,6 +326,12 @@ void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool 
     for (size_t li = 0; li < m.layers.size(); ++li) {
         KxLayer& l = m.layers[li];
         const KxLayerCfg& c = l.c;
+        if (m.cfg.family == KX_FAMILY_DEGAVIK) {
+            dg_enqueue_layer(s, l, rows, nslot_grid, decode, prof);
+            if (m.dbg_layers && !use_graph)
+                CK(cudaMemcpyAsync(m.dbg_layers + li * (size_t)maxT * W, m.x, (size_t)maxT * W * 4, cudaMemcpyDeviceToDevice, s));
+            continue;
+        }
         NormShiftParams ns{m.x, m.h, m.hs, l.mu, l.shift_state, l.gain, m.cfg.eps, W, mv};
         launch_k(norm_shift_kernel, dim3(rows), dim3(NORM_THREADS), 0, ns, KC_LN, s, prof);
         launch_k(shift_commit_kernel, dim3(nslot_grid), dim3(NORM_THREADS), 0, ns, KC_LN, s, prof);
@@ -397,7 +416,7 @@ void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool 
         if (m.dbg_layers && !use_graph)
             CK(cudaMemcpyAsync(m.dbg_layers + li * (size_t)maxT * W, m.x, (size_t)maxT * W * 4, cudaMemcpyDeviceToDevice, s));
     }
-    FinalNormParams fn{m.x, m.hn, d_hidden, m.final_gain, m.cfg.eps, W, mv};
+    FinalNormParams fn{m.x, m.hn, d_hidden, m.final_gain, m.cfg.eps, W, mv, m.final_w};
     launch_k(final_norm_kernel, dim3(rows), dim3(NORM_THREADS), 0, fn, KC_LN, s, prof);
     if (rrows > 0) {
         LinParams ph = lin(m.hn, W, m.head, d_logits, V, V, W);
@@ -423,7 +442,7 @@ void b200rwkv_engine::kx_fill_step(int* hm, const std::vector<int>& slots, const
     int T = 0, nch = 0, nupd = 0, ctx_max = 1;
     bool dec = true;
     for (int c : counts) dec = dec && c == 1;
-    const int QB = dec ? 1 : 4;
+    const int QB = dec ? 1 : m.qb_prompt;
     // hand out pages first: the step either fits or fails as a whole
     size_t need = 0;
     for (size_t i = 0; i < slots.size(); ++i) {
@@ -497,7 +516,7 @@ void b200rwkv_engine::kx_run_step(int T, int R, bool decode, int nsplit) {
     launch_total += graph_launches[key];
 }
 
-// ---- sequence memory <-> flat record: [4 header floats][per layer: shift W | gla state | cache rows x D] ----
+// ---- sequence memory <-> flat record: [4 header floats][per layer: its fixed blocks (shift row, recurrent state, ...) | cache rows x D] ----
 void b200rwkv_engine::kx_release(int slot) {
     Kemirax& m = *kx;
     for (int pg : m.pages[slot]) m.free_pages.push_back(pg);
@@ -542,18 +561,14 @@ void b200rwkv_engine::kx_xfer(int slot, float* rec, int ctx_rows, bool import, i
         o += cnt;
     };
     for (KxLayer& l : m.layers) {
-        copy(l.shift_state + (size_t)slot * W, W);
-        if (l.c.mixer == KX_GLA) {
-            const size_t sz = (size_t)l.c.heads * l.c.dim * l.c.vdim;
-            copy(l.gla_state + (size_t)slot * sz, sz);
-        } else if (l.c.kv_from < 0) {
-            const int D = l.c.kv_rank + l.c.rot_dim;
+        for (const KxLayer::Block& b : l.fixed) copy(b.base + (size_t)slot * b.per_slot, b.per_slot);
+        if (l.cache_D > 0) {
             if (n > 0) {
-                KxRowsParams rp{rec + o, l.cache, m.d_table + (size_t)slot * m.npages, m.page, D, n, import};
+                KxRowsParams rp{rec + o, l.cache, m.d_table + (size_t)slot * m.npages, m.page, l.cache_D, n, import};
                 kx_cache_rows_kernel<<<n, 128, 0, stream>>>(rp);
                 CK(cudaGetLastError());
             }
-            o += (size_t)ctx_rows * D;
+            o += (size_t)ctx_rows * l.cache_D;
         }
     }
 }
@@ -563,27 +578,19 @@ static void kx_relayout(const Kemirax& m, const float* src, int src_rows, float*
     size_t a = 4, b = 4;
     memset(dst, 0, 16);                                    // header: the caller writes the token count
     for (const KxLayer& l : m.layers) {
-        memcpy(dst + b, src + a, (size_t)m.W * 4); a += m.W; b += m.W;
-        if (l.c.mixer == KX_GLA) {
-            const size_t sz = (size_t)l.c.heads * l.c.dim * l.c.vdim;
-            memcpy(dst + b, src + a, sz * 4); a += sz; b += sz;
-        } else if (l.c.kv_from < 0) {
-            const size_t D = (size_t)l.c.kv_rank + l.c.rot_dim;
-            memcpy(dst + b, src + a, (size_t)n * D * 4);
-            a += (size_t)src_rows * D; b += (size_t)dst_rows * D;
+        for (const KxLayer::Block& blk : l.fixed) { memcpy(dst + b, src + a, blk.per_slot * 4); a += blk.per_slot; b += blk.per_slot; }
+        if (l.cache_D > 0) {
+            memcpy(dst + b, src + a, (size_t)n * l.cache_D * 4);
+            a += (size_t)src_rows * l.cache_D; b += (size_t)dst_rows * l.cache_D;
         }
     }
 }
 
-// an empty sequence in `slot`: pages back to the pool, shift rows and recurrent states zero
+// an empty sequence in `slot`: pages back to the pool, the fixed blocks (shift rows, recurrent states, convolution tails) zero
 void b200rwkv_engine::kx_reset(int slot) {
     Kemirax& m = *kx;
     kx_release(slot);
-    for (KxLayer& l : m.layers) {
-        CK(cudaMemsetAsync(l.shift_state + (size_t)slot * m.W, 0, (size_t)m.W * 4, stream));
-        if (l.c.mixer == KX_GLA) {
-            const size_t sz = (size_t)l.c.heads * l.c.dim * l.c.vdim;
-            CK(cudaMemsetAsync(l.gla_state + (size_t)slot * sz, 0, sz * 4, stream));
-        }
-    }
+    for (KxLayer& l : m.layers)
+        for (const KxLayer::Block& b : l.fixed)
+            if (b.per_slot) CK(cudaMemsetAsync(b.base + (size_t)slot * b.per_slot, 0, b.per_slot * 4, stream));
 }

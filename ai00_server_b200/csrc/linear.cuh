@@ -14,8 +14,8 @@
 //   lin_skinny_kernel        exact precision, a few rows: one warp per output pair, weight rows streamed as 16-byte loads, f32
 //                            FMA.
 //
-// Epilogues (fused): bias, sigmoid / silu, a per-row scale, accumulate-into-residual through a gate, and the clamped gated
-// unit of the experts on interleaved (gate, up) output pairs.
+// Epilogues (fused): bias, sigmoid / silu, a per-row scale, accumulate-into-residual through a gate, and the gated units
+// (clamped, or plain silu(g) * u) on interleaved (gate, up) output pairs.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -28,6 +28,7 @@ enum LinEpi {
     LE_SIGMOID = 1,     // Y = sigmoid(acc + bias)
     LE_GATED_ADD = 2,   // Y += gate[r, n] * acc          (residual accumulate; every element has one writer)
     LE_GLU_CLAMP = 3,   // outputs (2i, 2i+1) = (g, u): Y[r, i] = min(g, lim) * sigmoid(1.702 min(g, lim)) * (clamp(u, -lim, lim) + 1)
+    LE_GLU_SILU = 4,    // outputs (2i, 2i+1) = (g, u): Y[r, i] = g * sigmoid(g) * u
 };
 
 struct LinParams {
@@ -63,6 +64,10 @@ __device__ __forceinline__ void lin_store(const LinParams& p, int g, int yrow, i
     float* Y = p.Y + g * p.y_gstride;
     if (p.epi == LE_GLU_CLAMP) {                       // n is even: (gate, up) pair -> column n / 2
         Y[(size_t)yrow * p.ldy + (n >> 1)] = lin_glu(a0, a1, p.limit);
+        return;
+    }
+    if (p.epi == LE_GLU_SILU) {
+        Y[(size_t)yrow * p.ldy + (n >> 1)] = a0 * lin_sigmoid(a0) * a1;
         return;
     }
     const float* b = p.bias ? p.bias + (size_t)g * p.N : nullptr;

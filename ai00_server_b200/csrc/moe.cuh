@@ -27,7 +27,12 @@ struct MoeRouteParams {
     int* sel;                                 // [T][top] expert index
     float* wgt;                               // [T][top]
     MetaView meta;
+    int mode = 0;                             // MOE_SOFTMAX_ALL | MOE_TOP_LOGITS
 };
+
+// MOE_SOFTMAX_ALL: probabilities over all outputs, choice by probability + bias, weights = the chosen probabilities as they are.
+// MOE_TOP_LOGITS:  bias is part of the logits; the `top` largest logits are chosen, weights = softmax over the chosen logits only.
+enum MoeRouteMode { MOE_SOFTMAX_ALL = 0, MOE_TOP_LOGITS = 1 };
 
 constexpr int MOE_ROUTE_THREADS = 256;
 __host__ __device__ inline size_t moe_route_smem(int K, int NE) { return ((size_t)K + NE) * sizeof(float); }
@@ -63,10 +68,38 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const MoeR
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane == 0) z[e] = acc;
+        if (lane == 0) z[e] = acc + (p.mode == MOE_TOP_LOGITS && p.bias ? p.bias[e] : 0.f);
     }
     __syncthreads();
     if (warp != 0) return;
+    if (p.mode == MOE_TOP_LOGITS) {
+        unsigned long long taken = 0ull;
+        float zs[MOE_MAX_TOP];
+        float top_max = -CUDART_INF_F;
+        for (int k = 0; k < p.top; ++k) {
+            float best = -CUDART_INF_F; int bi = 0x7fffffff;
+            for (int e = lane, i = 0; e < p.NE; e += 32, ++i) {
+                if ((taken >> i) & 1ull) continue;
+                const float c = z[e];
+                if (c > best || (c == best && e < bi)) { best = c; bi = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+            }
+            if ((bi & 31) == lane) taken |= 1ull << (bi >> 5);
+            if (lane == 0) p.sel[(size_t)t * p.top + k] = bi;
+            zs[k] = best;
+            if (k == 0) top_max = best;
+        }
+        float sum = 0.f;
+        for (int k = 0; k < p.top; ++k) sum += expf(zs[k] - top_max);
+        if (lane == 0)
+            for (int k = 0; k < p.top; ++k) p.wgt[(size_t)t * p.top + k] = expf(zs[k] - top_max) / sum;
+        return;
+    }
     float mx = -CUDART_INF_F;
     for (int e = lane; e < p.NE; e += 32) mx = fmaxf(mx, z[e]);
 #pragma unroll

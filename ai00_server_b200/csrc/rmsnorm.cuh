@@ -4,7 +4,9 @@
 //                          h_prev = the previous token's h: the row before it in this step, or the sequence's shift state);
 //   shift_commit_kernel    the last token of every sequence in the step leaves its h as the new shift state
 //   rms_rows_kernel        y[r, c*w .. c*w+w) = x / rms(x over the w-wide chunk) * weight[w]   (per-chunk norm with a weight vector)
-//   final_norm_kernel      rows that want logits: x[out_tok[r]] / rms * g  -> compact [R, W] head operand (+ all hidden rows)
+//   final_norm_kernel      rows that want logits: x[out_tok[r]] / rms * g  -> compact [R, W] head operand (+ all hidden rows);
+//                          g = one scalar gain or a weight vector
+//   norm_add_kernel        x += y / rms(y) * w: the norm sits on a sublayer's output (optionally combining routed expert rows first)
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -119,6 +121,7 @@ struct FinalNormParams {
     float gain, eps;
     int W;
     MetaView meta;
+    const float* weight = nullptr;   // [W] per-channel weight instead of the scalar gain
 };
 
 __global__ void __launch_bounds__(NORM_THREADS) final_norm_kernel(const FinalNormParams p) {
@@ -134,8 +137,57 @@ __global__ void __launch_bounds__(NORM_THREADS) final_norm_kernel(const FinalNor
     float ss = 0.f;
     for (int c = threadIdx.x; c < W; c += blockDim.x) ss = fmaf(xr[c], xr[c], ss);
     ss = rms_block_sum(ss, red);
-    const float r = p.gain / sqrtf(ss / (float)W + p.eps);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) p.y[(size_t)row * W + c] = xr[c] * r;
+    const float r = (p.weight ? 1.f : p.gain) / sqrtf(ss / (float)W + p.eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) p.y[(size_t)row * W + c] = xr[c] * r * (p.weight ? p.weight[c] : 1.f);
+}
+
+// Norm on a sublayer's OUTPUT, added to the residual:  x[t] += y[t] / rms(y[t]) * w.  The sublayer's output row y is either a
+// plain row, or the weighted sum of a routed feed-forward's chosen expert rows plus its shared expert (then this is also the
+// experts' combine step).  All f32.
+struct NormAddParams {
+    float* x;                 // [T, W] residual, accumulated in place
+    const float* y;           // [T, W] sublayer output (nullptr with rows)
+    const float* rows;        // [T * top, W] expert outputs in compact rows (nullptr: y)
+    const int* row_of; const float* wgt; int top;
+    const float* shared;      // [T, W] added to the experts' sum (nullptr: none)
+    const float* weight;      // [W]
+    float eps;
+    int W;
+    MetaView meta;
+};
+
+constexpr int NORM_ADD_MAX_TOP = 8;
+
+__global__ void __launch_bounds__(NORM_THREADS) norm_add_kernel(const NormAddParams p) {
+    __shared__ float red[32];
+    extern __shared__ __align__(16) float norm_add_row[];      // [W] the combined row (expert form only)
+    const int t = blockIdx.x;
+    if (t >= p.meta.T()) return;
+    const int W = p.W;
+    float ss = 0.f;
+    if (p.rows) {
+        int rw[NORM_ADD_MAX_TOP]; float wg[NORM_ADD_MAX_TOP];
+#pragma unroll
+        for (int k = 0; k < NORM_ADD_MAX_TOP; ++k)
+            if (k < p.top) { rw[k] = p.row_of[(size_t)t * p.top + k]; wg[k] = p.wgt[(size_t)t * p.top + k]; }
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            float f = 0.f;
+#pragma unroll
+            for (int k = 0; k < NORM_ADD_MAX_TOP; ++k)
+                if (k < p.top) f = fmaf(wg[k], p.rows[(size_t)rw[k] * W + c], f);
+            if (p.shared) f += p.shared[(size_t)t * W + c];
+            norm_add_row[c] = f;
+            ss = fmaf(f, f, ss);
+        }
+    } else {
+        for (int c = threadIdx.x; c < W; c += blockDim.x) { const float f = p.y[(size_t)t * W + c]; ss = fmaf(f, f, ss); }
+    }
+    ss = rms_block_sum(ss, red);
+    const float r = 1.f / sqrtf(ss / (float)W + p.eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float f = p.rows ? norm_add_row[c] : p.y[(size_t)t * W + c];
+        p.x[(size_t)t * W + c] += f * r * p.weight[c];
+    }
 }
 
 }  // namespace b200

@@ -101,7 +101,9 @@ typedef struct {
     int32_t quant_layers;
     int32_t quant_type;               /* B200RWKV_QUANT_* */
     /* Model families that are described by a config.json beside the weights (architecture "Kemirax": parallel blocks of latent
-     * attention / gated linear attention + routed experts, bf16 weights): the JSON text, borrowed during the call.  NULL: the
+     * attention / gated linear attention + routed experts; architecture "Degavik": blocks normed on the sublayer outputs with
+     * retention / gated delta rule / windowed attention mixers and dense or routed feed-forwards; bf16 weights): the JSON text,
+     * borrowed during the call.  NULL: the
      * family is recognised from the tensor names (RWKV v5 / v6 / v7).  Such models keep an attention cache in pages of
      * `kv_page` tokens (0 = 64) drawn from a pool sized for `kv_tokens` tokens over all live sequences (0 = 4096 per slot);
      * precision 0 = bf16 tensor-core products with f32 accumulation, 1 = every product in plain f32.  Their steps hold up to
@@ -112,6 +114,7 @@ typedef struct {
     int32_t kv_page;
 } b200rwkv_options;
 #define B200RWKV_ARCH_KEMIRAX 100     /* b200rwkv_info.version of that family (num_head / head_size are per layer there: 0) */
+#define B200RWKV_ARCH_DEGAVIK 101
 #define B200RWKV_QUANT_NONE 0
 #define B200RWKV_QUANT_INT8 1         /* blocks of 128 inputs: f16 (min, max) + 8-bit codes */
 #define B200RWKV_QUANT_NF4 2          /* blocks of 64 inputs: f16 absmax + 4-bit NormalFloat codes */
