@@ -384,3 +384,103 @@ def make_kemirax(layers: list, width: int = 64, vocab: int = 96, eps: float = 1e
     bits = {k: to_bf16_bits(np.asarray(v, np.float32).reshape(np.shape(v))) for k, v in t.items()}
     rounded = {k: (b.astype(np.uint32) << 16).view(np.float32).reshape(np.shape(t[k])).astype(np.float64) for k, b in bits.items()}
     return json.dumps(cfg).encode(), pack_st_bf16(t), rounded
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Degavik family (config.json + bf16 safetensors): random weights for tests and bench.py
+# ----------------------------------------------------------------------------------------------------------------------
+def degavik_layer(kind: str, *, heads=4, kv_heads=None, dim=16, vdim=16, rot_dims=None, base=10000.0, decay=None, conv=3, window=8,
+                  keep_first=2, scale=None, softcap=20.0, mlp="dense", ff=48, experts=4, top=2, shared_ff=32, weights_of=None) -> dict:
+    """One entry of config['layers'].  kind: 'retention' | 'channel_delta' | 'attention'; mlp: 'dense' | 'moe' | None."""
+    if kind == "retention":
+        mixer = {"heads": heads, "dim": dim, "vdim": vdim, "rot": {"base": float(base), "dims": int(dim if rot_dims is None else rot_dims)},
+                 "decay": [float(d) for d in (decay if decay is not None else 1.0 - 2.0 ** (-2.0 - np.arange(heads) * 6.0 / max(heads, 1)))]}
+    elif kind == "channel_delta":
+        mixer = {"heads": heads, "kv_heads": int(kv_heads or heads), "dim": dim, "vdim": vdim, "conv": int(conv)}
+    elif kind == "attention":
+        mixer = {"heads": heads, "kv_heads": int(kv_heads or heads), "dim": dim, "vdim": vdim,
+                 "rot": {"base": float(base), "dims": int(dim if rot_dims is None else rot_dims)},
+                 "scale": float(scale if scale is not None else dim ** -0.5), "softcap": float(softcap),
+                 "mask": {"size": int(window), "keep_first": int(keep_first)}}
+    else:
+        raise ValueError(kind)
+    layer = {"type": kind, "mixer": mixer, "mlp": None}
+    if mlp == "dense":
+        layer["mlp"] = {"kind": "dense", "ff": int(ff)}
+    elif mlp == "moe":
+        layer["mlp"] = {"kind": "moe", "router": {"experts": int(experts), "top": int(top)}, "expert": {"ff": int(ff)}}
+        if shared_ff:
+            layer["mlp"]["shared"] = {"ff": int(shared_ff)}
+    if weights_of is not None:
+        layer["weights_of"] = int(weights_of)
+    return layer
+
+
+def make_degavik(layers: list, width: int = 64, vocab: int = 96, eps: float = 1e-5, seed: int = 0, low_rank: int = 8, arrays: bool = True):
+    """(config.json bytes, safetensors image, dict of float64 arrays holding the bf16-rounded values, or None when `arrays` is
+    off) for a random model of the family.  Layers with `weights_of` get no tensors."""
+    rng = np.random.default_rng(seed)
+    W = width
+    t = {}
+
+    def mat(n, k, g=1.0):
+        return (rng.standard_normal((n, k)) * (g / np.sqrt(k))).astype(np.float32)
+
+    def unit(p, ff):
+        t[p + "gate"] = mat(ff, W, 2.0)
+        t[p + "up"] = mat(ff, W, 2.0)
+        t[p + "down"] = mat(W, ff)
+
+    t["embed"] = rng.standard_normal((vocab, W)).astype(np.float32)
+    for i, l in enumerate(layers):
+        if l.get("weights_of") is not None:
+            continue
+        p, m = "l%d." % i, l["mixer"]
+        H, dk, dv = m["heads"], m["dim"], m["vdim"]
+        G = m.get("kv_heads", H)
+        t[p + "norm1"] = rng.uniform(0.5, 1.5, W).astype(np.float32)
+        if l["type"] == "retention":
+            for n, rows in (("q", H * dk), ("k", H * dk), ("v", H * dv), ("g", H * dv)):
+                t[p + "mix." + n] = mat(rows, W, 2.0 if n in "qk" else 1.0)
+        elif l["type"] == "channel_delta":
+            for n, rows in (("q", G * dk), ("k", G * dk), ("v", H * dv)):
+                t[p + "mix." + n] = mat(rows, W, 2.0)
+                t[p + "mix." + n + ".conv"] = (rng.standard_normal((rows, m["conv"])) * 0.6).astype(np.float32)
+            t[p + "mix.b"] = mat(H, W, 2.0)
+            t[p + "mix.A_log"] = rng.uniform(-4.0, 0.0, H).astype(np.float32)
+            t[p + "mix.norm"] = rng.uniform(0.5, 1.5, dv).astype(np.float32)
+            t[p + "mix.a1"] = mat(low_rank, W)
+            t[p + "mix.a2"] = mat(H * dk, low_rank, 2.0)
+            t[p + "mix.dt_bias"] = rng.uniform(-4.0, 1.0, H * dk).astype(np.float32)
+            t[p + "mix.g1"] = mat(low_rank, W)
+            t[p + "mix.g2"] = mat(H * dv, low_rank, 2.0)
+        else:
+            t[p + "mix.q"] = mat(H * dk, W, 2.0)
+            t[p + "mix.k"] = mat(G * dk, W, 2.0)
+            t[p + "mix.v"] = mat(G * dv, W)
+            t[p + "mix.q.norm"] = rng.uniform(0.5, 1.5, dk).astype(np.float32)
+            t[p + "mix.k.norm"] = rng.uniform(0.5, 1.5, dk).astype(np.float32)
+            t[p + "mix.talk"] = (np.eye(H) + 0.3 * rng.standard_normal((H, H))).astype(np.float32)
+            t[p + "mix.temp"] = rng.uniform(0.5, 1.5, H).astype(np.float32)
+        t[p + "mix.o"] = mat(W, H * dv)
+        f = l.get("mlp")
+        if f:
+            t[p + "norm2"] = rng.uniform(0.5, 1.5, W).astype(np.float32)
+            if f["kind"] == "dense":
+                unit(p + "mlp.", f["ff"])
+            else:
+                E = f["router"]["experts"]
+                t[p + "mlp.router"] = mat(E, W, 2.0)
+                t[p + "mlp.router.b"] = rng.uniform(-0.5, 0.5, E).astype(np.float32)
+                for e in range(E):
+                    unit(p + "mlp.e%d." % e, f["expert"]["ff"])
+                if f.get("shared"):
+                    unit(p + "mlp.shared.", f["shared"]["ff"])
+    t["final.norm"] = rng.uniform(0.5, 1.5, W).astype(np.float32)
+    t["head"] = mat(vocab, W)
+    cfg = {"architecture": "Degavik", "layers": layers, "norm": {"eps": eps}, "vocab": vocab, "width": W}
+    if not arrays:
+        return json.dumps(cfg).encode(), pack_st_bf16(t), None
+    bits = {k: to_bf16_bits(np.asarray(v, np.float32).reshape(np.shape(v))) for k, v in t.items()}
+    rounded = {k: (b.astype(np.uint32) << 16).view(np.float32).reshape(np.shape(t[k])).astype(np.float64) for k, b in bits.items()}
+    return json.dumps(cfg).encode(), pack_st_bf16(t), rounded
