@@ -29,6 +29,14 @@ struct MetaView {
     __host__ __device__ static size_t ints(int maxT, int maxS) { return 8 + 6 * (size_t)maxT + 3 * (size_t)maxS; }
 };
 
+// cosine and sine of position * frequency: the product and its reduction to [-pi, pi] in double (a float product is off by
+// 1e-4 rad at a few thousand tokens), the functions themselves in f32 on the reduced angle
+__device__ __forceinline__ void rot_cos_sin(int pos, double freq, float& cs, float& sn) {
+    double a = (double)pos * freq;
+    a -= 6.283185307179586 * rint(a * 0.15915494309189535);
+    sincosf((float)a, &sn, &cs);
+}
+
 // ---------------------------------------------------------------------------------------
 // "A16" activation layout: the f16 operand of every projection, stored so that (a) the slice a GEMM stage needs -- one
 // 128-wide k block of ALL tokens of the step -- is ONE contiguous run (one bulk TMA copy) and (b) that run IS the UMMA

@@ -128,10 +128,10 @@ void b200rwkv_engine::dg_load(const StFile& st, KxSizes& z) {
             l.decay = kx_up32(d);
         }
         if (c.mixer == KX_RETENTION || c.mixer == KX_WINDOW) {
-            std::vector<float> fr;
-            float mag;
-            kx_rot_table(c.rot, fr, mag);
-            l.freq = kx_up32(fr);
+            std::vector<double> fr(std::max(c.rot.dims / 2, 1), 0.0);
+            for (int f = 0; f < c.rot.dims / 2; ++f) fr[f] = std::pow(c.rot.base, -2.0 * f / c.rot.dims);
+            l.freq_d = (double*)dalloc(fr.size() * 8, false);
+            CK(cudaMemcpy(l.freq_d, fr.data(), fr.size() * 8, cudaMemcpyHostToDevice));
         }
         if (c.mixer == KX_DELTA) {
             const size_t tail = (size_t)(c.taps - 1) * l.conv_C;
@@ -143,8 +143,8 @@ void b200rwkv_engine::dg_load(const StFile& st, KxSizes& z) {
         if (c.mixer == KX_WINDOW) {
             l.cache_D = G_ * (dk + dv);
             l.cache = (float*)dalloc((size_t)m.npages * m.page * l.cache_D * 4);
-            while (qb > 1 && window_attn_smem(qb, H_, dk, dv) > 160 * 1024) qb /= 2;
-            REQUIRE(window_attn_smem(1, H_, dk, dv) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "attention heads too large for shared memory");
+            while (qb > 1 && window_attn_smem(qb, H_, dk, dv, 1) > 128 * 1024) qb /= 2;
+            REQUIRE(window_attn_smem(1, H_, dk, dv, 1) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "attention heads too large for shared memory");
             z.n_q = std::max(z.n_q, (size_t)H_ * dk);
         }
         z.n_pr = std::max(z.n_pr, (size_t)l.proj_n); z.n_vout = std::max(z.n_vout, (size_t)H_ * dv);
@@ -158,6 +158,11 @@ void b200rwkv_engine::dg_load(const StFile& st, KxSizes& z) {
         }
     }
     m.qb_prompt = qb;
+    for (KxLayer& l : m.layers)
+        if (l.c.mixer == KX_WINDOW) {              // as many key / value heads per tile load as fit beside the chunk's rows
+            l.wa_gt = l.c.kv_heads;
+            while (l.wa_gt > 1 && window_attn_smem(qb, l.c.heads, l.c.dim, l.c.vdim, l.wa_gt) > 160 * 1024) l.wa_gt = (l.wa_gt + 1) / 2;
+        }
     CK(cudaFuncSetAttribute(retention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     CK(cudaFuncSetAttribute(delta_rule_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     CK(cudaFuncSetAttribute(window_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -166,7 +171,7 @@ void b200rwkv_engine::dg_load(const StFile& st, KxSizes& z) {
 }
 
 // one layer: x += rms(mixer(x)) * w1, then x += rms(ff(x)) * w2
-void b200rwkv_engine::dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int nslot_grid, bool decode, Profiler* prof) {
+void b200rwkv_engine::dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int nslot_grid, bool decode, int nsplit, Profiler* prof) {
     Kemirax& m = *kx;
     const int W = m.W;
     MetaView mv{d_meta, maxT, S};
@@ -182,7 +187,7 @@ void b200rwkv_engine::dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int
     const int PN = l.proj_n;
     kx_lin(s, prof, lin(m.x, W, l.proj, m.pr, PN, PN, W), rows, 1);
     if (c.mixer == KX_RETENTION) {
-        RetentionParams rp{m.pr, m.pr + H_ * dk, m.pr + 2 * H_ * dk, m.pr + 2 * H_ * dk + H_ * dv, PN, l.rec_state, m.vout, H_ * dv, l.decay, l.freq,
+        RetentionParams rp{m.pr, m.pr + H_ * dk, m.pr + 2 * H_ * dk, m.pr + 2 * H_ * dk + H_ * dv, PN, l.rec_state, m.vout, H_ * dv, l.decay, l.freq_d,
                            H_, dk, dv, c.rot.dims, 1.f / sqrtf((float)dk), m.cfg.eps, mv, m.sm};
         launch_k(retention_kernel, dim3(H_, nslot_grid), dim3(rup(dv, 32)), retention_smem_bytes(dk, dv), rp, KC_WKV, s, prof);
     } else if (c.mixer == KX_DELTA) {
@@ -197,13 +202,14 @@ void b200rwkv_engine::dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int
         launch_k(delta_rule_kernel, dim3(H_, nslot_grid), dim3(rup(dv, 32)), delta_rule_smem_bytes(dk, dv), dp, KC_WKV, s, prof);
     } else {
         AttnPrepParams ap{m.pr, m.pr + H_ * dk, m.pr + H_ * dk + G_ * dk, PN, m.q, H_ * dk, l.cache, m.d_table, m.npages, m.page, l.qn_w, l.kn_w,
-                          l.temp, l.freq, H_, G_, dk, dv, c.rot.dims, c.scale, m.cfg.eps, mv, m.sm};
+                          l.temp, l.freq_d, H_, G_, dk, dv, c.rot.dims, c.scale, m.cfg.eps, mv, m.sm};
         launch_k(attn_prep_kernel, dim3(rows), dim3(128), 0, ap, KC_OTHER, s, prof);
         const int qb = decode ? 1 : m.qb_prompt;
         WindowAttnParams wp{m.q, H_ * dk, l.cache, m.d_table, m.npages, m.page, m.vout, H_ * dv, l.talk, H_, G_, dk, dv, c.window, c.keep_first,
-                            c.softcap, qb, mv, m.sm};
-        launch_k(window_attn_kernel, dim3(decode ? rows : cdiv(rows, qb) + nslot_grid), dim3(WA_THREADS), window_attn_smem(qb, H_, dk, dv), wp,
-                 KC_WKV, s, prof);
+                            c.softcap, qb, l.wa_gt, nsplit, mv, m.sm};
+        launch_cluster = nsplit;
+        launch_k(window_attn_kernel, dim3((decode ? rows : cdiv(rows, qb) + nslot_grid) * nsplit), dim3(WA_THREADS),
+                 window_attn_smem(qb, H_, dk, dv, l.wa_gt), wp, KC_WKV, s, prof);
     }
     kx_lin(s, prof, lin(m.vout, H_ * dv, l.o, m.y, W, W, H_ * dv), rows, 1);
     {

@@ -521,7 +521,7 @@ struct b200rwkv_engine {
     void kx_build(const StFile& st, const char* cfg_json, size_t cfg_len);
     void kx_load(const StFile& st, KxSizes& z);
     void dg_load(const StFile& st, KxSizes& z);                   // Degavik family (degavik_engine.cuh)
-    void dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int nslot_grid, bool decode, Profiler* prof);
+    void dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int nslot_grid, bool decode, int nsplit, Profiler* prof);
     __nv_bfloat16* kx_up16(const std::vector<uint16_t>& v);
     float* kx_up32(const std::vector<float>& v);
     void kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int rows, int groups, bool force_exact = false);

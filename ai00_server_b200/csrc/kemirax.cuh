@@ -247,6 +247,8 @@ struct KxLayer {
     float *a_log = nullptr, *conv_w = nullptr, *conv_tail = nullptr;   // delta rule: [H], [C][taps], [S][taps - 1][C]
     int g_rank = 0, conv_C = 0;
     float *qn_w = nullptr, *kn_w = nullptr, *talk = nullptr, *temp = nullptr;   // windowed attention
+    double* freq_d = nullptr;                                    // rotary frequencies in double (retention, windowed attention)
+    int wa_gt = 1;                                               // key / value heads per tile load of the attention kernel
     float* rec_state = nullptr;                                  // retention / delta rule: [S][H][dk][dv]
     int cache_D = 0;                                             // floats per cached token when the layer owns a pool
     // per-sequence memory of fixed size, in the order of the flat state record

@@ -211,7 +211,6 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
     d_meta = (int*)dalloc(meta_ints * 4);
     CK(cudaMallocHost(&h_meta, meta_ints * 4 * META_RING));
     memset(h_meta, 0, meta_ints * 4 * META_RING);
-    MetaView mv{d_meta, maxT, S};
     m.sm = SeqMeta{d_meta + mv_ints, maxT};
 
     // ---- pages ----
@@ -327,7 +326,7 @@ void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool 
         KxLayer& l = m.layers[li];
         const KxLayerCfg& c = l.c;
         if (m.cfg.family == KX_FAMILY_DEGAVIK) {
-            dg_enqueue_layer(s, l, rows, nslot_grid, decode, prof);
+            dg_enqueue_layer(s, l, rows, nslot_grid, decode, nsplit, prof);
             if (m.dbg_layers && !use_graph)
                 CK(cudaMemcpyAsync(m.dbg_layers + li * (size_t)maxT * W, m.x, (size_t)maxT * W * 4, cudaMemcpyDeviceToDevice, s));
             continue;
@@ -479,6 +478,14 @@ void b200rwkv_engine::kx_fill_step(int* hm, const std::vector<int>& slots, const
         const int ctas = std::max(1, nch * hg_min), tiles = cdiv(ctx_max, LA_KT);
         while (ns < m.max_split && ctas * ns < 2 * num_sms && tiles / (ns * 2) >= 2) ns *= 2;
     }
+    if (m.cfg.family == KX_FAMILY_DEGAVIK) {               // CTAs per attention chunk (a cluster): the keys a chunk can see, in tiles
+        int seen = 0;
+        for (const KxLayer& l : m.layers)
+            if (l.c.mixer == KX_WINDOW) seen = std::max(seen, std::min(ctx_max, l.c.window + l.c.keep_first + QB));
+        const int tiles = cdiv(seen, WA_KT);
+        ns = 1;
+        while (ns < 8 && std::max(1, nch) * ns < num_sms && tiles / (ns * 2) >= 1) ns *= 2;
+    }
     *decode = dec; *nsplit = ns;
 }
 
@@ -540,7 +547,6 @@ __global__ void kx_cache_rows_kernel(const KxRowsParams p) {
 // export (import = false): slot -> record with `ctx_rows` cache rows per layer; import: record holding `n` tokens -> slot
 void b200rwkv_engine::kx_xfer(int slot, float* rec, int ctx_rows, bool import, int n) {
     Kemirax& m = *kx;
-    const int W = m.W;
     if (import) {
         kx_release(slot);
         REQUIRE(n >= 0 && n <= ctx_rows, B200RWKV_ERR_INVALID, "state record holds more tokens than it has rows");

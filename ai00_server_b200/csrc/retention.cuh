@@ -4,8 +4,8 @@
 // head), k scaled after the rotation.  The read-out is divided by its root mean square over the value width (no weight) and
 // multiplied by silu of a gate projection.  One CTA per (head, sequence of the step): the [dk, dv] f32 state stays in shared
 // memory for the sequence's tokens of this step, column j belongs to thread j (decay, rank-1 update and read-out in one pass
-// over the column, no cross-thread traffic), and is loaded from / stored to the sequence's slot once per step.  Positions,
-// angles, state, read-out and norm are f32.
+// over the column, no cross-thread traffic), and is loaded from / stored to the sequence's slot once per step.  State,
+// read-out and norm are f32; the rotation angle is formed and reduced in double (rot_cos_sin).
 #pragma once
 #include <cuda_runtime.h>
 #include "common.cuh"
@@ -19,7 +19,7 @@ struct RetentionParams {
     float* state;                                 // [S][H][dk][dv] of this layer
     float* out; int ldo;                          // [T, H * dv]: normed, gated
     const float* decay;                           // [H]
-    const float* freq;                            // [rot_dims / 2]
+    const double* freq;                           // [rot_dims / 2]
     int H, dk, dv, rot_dims;
     float k_scale, eps;
     MetaView meta; SeqMeta sm;
@@ -49,14 +49,14 @@ __global__ void retention_kernel(const RetentionParams p) {
     const float lam = p.decay[h];
     for (int t = t0; t < t0 + nt; ++t) {
         __syncthreads();
-        const float pos = (float)p.sm.tok_pos()[t];
+        const int ipos = p.sm.tok_pos()[t];
         const float* qr = p.q + (size_t)t * p.ld + (size_t)h * dk;
         const float* kr = p.k + (size_t)t * p.ld + (size_t)h * dk;
         for (int i = j; i < dk; i += blockDim.x) {
             if (i >= p.rot_dims) { sq[i] = qr[i]; sk[i] = kr[i] * p.k_scale; continue; }
             const int f = i < half ? i : i - half;
-            const float a = pos * p.freq[f];
-            const float cs = cosf(a), sn = sinf(a);
+            float cs, sn;
+            rot_cos_sin(ipos, p.freq[f], cs, sn);
             const float qu = qr[f], qv = qr[f + half], ku = kr[f], kv = kr[f + half];
             sq[i] = i < half ? qu * cs - qv * sn : qv * cs + qu * sn;
             sk[i] = (i < half ? ku * cs - kv * sn : kv * cs + ku * sn) * p.k_scale;

@@ -13,10 +13,14 @@
 //
 //   attn_prep_kernel     per token: q heads = rms(q) * w_q, rotated, times scale * temp_h -> q buffer;  k heads = rms(k) * w_k,
 //                        rotated, and v -> the cache row of (slot, position).  Rotation pairs entry 2i with 2i + 1 on the first
-//                        `dims` entries of a head; angle = position * frequency in f32.
-//   window_attn_kernel   one CTA per chunk of consecutive tokens of one sequence (SeqMeta chunks), all heads; 32-key tiles of one
-//                        key / value head at a time in shared memory; scores, softmax, mix and the weighted sums in f32.
+//                        `dims` entries of a head.
+//   window_attn_kernel   a cluster of 1..8 CTAs per chunk of consecutive tokens of one sequence (SeqMeta chunks), all heads; the
+//                        32-key tiles of the walk are dealt out among the cluster's CTAs (decode steps and short steps would
+//                        otherwise run on a handful of SMs); the per-row maxima / sums after the first walk and the partial
+//                        outputs after the second are combined through distributed shared memory in rank order.  A warp scores
+//                        four rows of one key / value head against a key at a time.  Scores, softmax, mix and sums in f32.
 #pragma once
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <math_constants.h>
 #include "common.cuh"
@@ -31,7 +35,7 @@ struct AttnPrepParams {
     const int* table; int stride; int page;
     const float* wq; const float* wk;             // [dk] norm weights
     const float* temp;                            // [H]
-    const float* freq;                            // [dims / 2]
+    const double* freq;                           // [dims / 2]
     int H, G, dk, dv, dims;
     float scale, eps;
     MetaView meta; SeqMeta sm;
@@ -42,7 +46,6 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepParams p) 
     if (t >= p.meta.T()) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int slot = p.meta.tok_slot()[t], ipos = p.sm.tok_pos()[t];
-    const float pos = (float)ipos;
     const int D = p.G * (p.dk + p.dv);
     float* row = p.cache + ((size_t)p.table[(size_t)slot * p.stride + ipos / p.page] * p.page + ipos % p.page) * D;
     for (int hh = warp; hh < p.H + p.G; hh += nw) {
@@ -61,8 +64,8 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepParams p) 
             float val;
             if (i < p.dims) {
                 const int e = i & ~1;
-                const float a = pos * p.freq[i >> 1];
-                const float cs = cosf(a), sn = sinf(a);
+                float cs, sn;
+                rot_cos_sin(ipos, p.freq[i >> 1], cs, sn);
                 const float u = src[e] * r * w[e], v = src[e + 1] * r * w[e + 1];
                 val = (i & 1) ? v * cs + u * sn : u * cs - v * sn;
             } else {
@@ -86,20 +89,32 @@ struct WindowAttnParams {
     int window, keep;
     float cap;
     int qb;                                       // tokens per chunk the shared memory was sized for
+    int gt;                                       // key / value heads per tile load
+    int cl;                                       // CTAs per chunk (cluster size): the key tiles are dealt out among them
     MetaView meta; SeqMeta sm;
 };
 
 constexpr int WA_KT = 32;                          // keys per tile (one per lane in the score phase)
 constexpr int WA_THREADS = 256;
+constexpr int WA_RB = 4;                           // rows of one key / value head a warp works on together
 
-__host__ __device__ inline size_t window_attn_smem(int qb, int H, int dk, int dv) {
+__host__ __device__ inline size_t window_attn_smem(int qb, int H, int dk, int dv, int gt) {
     const size_t R = (size_t)qb * H, dmax = dk > dv ? dk : dv;
-    return (R * dk + R * dv + 2 * R * WA_KT + (size_t)WA_KT * (dmax + 1) + 2 * R + (size_t)H * H + 8) * sizeof(float);
+    return (R * dk + R * dv + 2 * R * WA_KT + (size_t)gt * WA_KT * (dmax + 1) + 4 * R + (size_t)H * H + 8) * sizeof(float);
+}
+
+// the tile `ti` of the key walk: segment 0 first, then segment 1
+__device__ __forceinline__ void wa_tile(int ti, int n0, const int* lo, const int* hi, int& j0, int& nk) {
+    const int sg = ti < n0 ? 0 : 1, k = ti < n0 ? ti : ti - n0;
+    j0 = lo[sg] + k * WA_KT;
+    nk = min(WA_KT, hi[sg] - j0);
 }
 
 __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAttnParams p) {
-    const int ch = blockIdx.x;
-    if (ch >= p.sm.n_chunks()) return;
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CL = p.cl, rank = blockIdx.x % CL, ch = blockIdx.x / CL;
+    if (ch >= p.sm.n_chunks()) return;             // the same for every CTA of a cluster
     const int t0 = p.sm.chunk_start()[ch], nq = p.sm.chunk_count()[ch];
     const int slot = p.meta.tok_slot()[t0];
     const int pos0 = p.sm.tok_pos()[t0], pos1 = pos0 + nq - 1;
@@ -112,10 +127,12 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
     float* sO = sQ + (size_t)Rcap * dk;           // [R][dv]
     float* sP = sO + (size_t)Rcap * dv;           // [R][KT] normalised weights of the tile
     float* sM = sP + (size_t)Rcap * WA_KT;        // [R][KT] mixed weights
-    float* sT = sM + (size_t)Rcap * WA_KT;        // [KT][ts] key or value tile of one head
-    float* sMax = sT + (size_t)WA_KT * ts;        // [R]
-    float* sSum = sMax + Rcap;                    // [R]
-    float* sMix = sSum + Rcap;                    // [H][H]
+    float* sT = sM + (size_t)Rcap * WA_KT;        // [gt][KT][ts] key or value tiles of gt heads
+    float* sMax = sT + (size_t)p.gt * WA_KT * ts; // [R] this CTA's running maximum / sum
+    float* sSum = sMax + Rcap;
+    float* sGMax = sSum + Rcap;                   // [R] the chunk's (all CTAs of the cluster)
+    float* sGSum = sGMax + Rcap;
+    float* sMix = sGSum + Rcap;                   // [H][H]
     for (int e = threadIdx.x; e < R * dk; e += WA_THREADS) {
         const int r = e / dk, i = e % dk;
         sQ[e] = p.q[(size_t)(t0 + r / H) * p.ldq + (size_t)(r % H) * dk + i];
@@ -124,39 +141,59 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
     for (int e = threadIdx.x; e < R; e += WA_THREADS) { sMax[e] = -CUDART_INF_F; sSum[e] = 0.f; }
     for (int e = threadIdx.x; e < H * H; e += WA_THREADS) sMix[e] = p.mix[e];
     // key ranges: the kept prefix [0, a_hi) and the window [b_lo, pos1]; one range when they touch
-    int seg_lo[2], seg_hi[2], nseg = 1;
+    int seg_lo[2] = {0, 0}, seg_hi[2] = {0, 0};
     {
         const int a_hi = min(p.keep, pos1 + 1), b_lo = max(0, pos0 - p.window + 1);
         if (a_hi <= 0) { seg_lo[0] = b_lo; seg_hi[0] = pos1 + 1; }
         else if (b_lo <= a_hi) { seg_lo[0] = 0; seg_hi[0] = pos1 + 1; }
-        else { seg_lo[0] = 0; seg_hi[0] = a_hi; seg_lo[1] = b_lo; seg_hi[1] = pos1 + 1; nseg = 2; }
+        else { seg_lo[0] = 0; seg_hi[0] = a_hi; seg_lo[1] = b_lo; seg_hi[1] = pos1 + 1; }
     }
+    const int n0 = (seg_hi[0] - seg_lo[0] + WA_KT - 1) / WA_KT, ntiles = n0 + (seg_hi[1] - seg_lo[1] + WA_KT - 1) / WA_KT;
     const int* tbl = p.table + (size_t)slot * p.stride;
+    const int nrg = nq * rep;                      // rows of one key / value head
+    const int nblk = (nrg + WA_RB - 1) / WA_RB;    // row blocks of one head
     __syncthreads();
     for (int pass = 0; pass < 2; ++pass) {
-        for (int sg = 0; sg < nseg; ++sg) {
-            for (int j0 = seg_lo[sg]; j0 < seg_hi[sg]; j0 += WA_KT) {
-                const int nk = min(WA_KT, seg_hi[sg] - j0);
-                const int jl = j0 + lane;
-                for (int c = 0; c < G; ++c) {
-                    __syncthreads();               // the tile buffer is free
-                    for (int kt = warp; kt < nk; kt += nw) {
-                        const int j = j0 + kt;
-                        const float* src = p.cache + ((size_t)tbl[j / p.page] * p.page + j % p.page) * D + (size_t)c * dk;
-                        for (int i = lane; i < dk; i += 32) sT[kt * ts + i] = src[i];
+        for (int ti = rank; ti < ntiles; ti += CL) {
+            int j0, nk;
+            wa_tile(ti, n0, seg_lo, seg_hi, j0, nk);
+            const int jl = j0 + lane;
+            for (int c0 = 0; c0 < G; c0 += p.gt) {
+                const int gn = min(p.gt, G - c0);
+                __syncthreads();                   // the tile buffer is free
+                for (int e = warp; e < gn * nk; e += nw) {
+                    const int cl_ = e / nk, kt = e % nk, j = j0 + kt;
+                    const float* src = p.cache + ((size_t)tbl[j / p.page] * p.page + j % p.page) * D + (size_t)(c0 + cl_) * dk;
+                    float* dst = sT + ((size_t)cl_ * WA_KT + kt) * ts;
+                    for (int i = lane; i < dk; i += 32) dst[i] = src[i];
+                }
+                __syncthreads();
+                for (int it = warp; it < gn * nblk; it += nw) {
+                    const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * WA_RB, nr = min(WA_RB, nrg - rr0);
+                    int rows[WA_RB];
+                    const float* qv[WA_RB];
+#pragma unroll
+                    for (int b = 0; b < WA_RB; ++b) {
+                        const int rr = rr0 + min(b, nr - 1);
+                        rows[b] = (rr / rep) * H + c * rep + rr % rep;
+                        qv[b] = sQ + (size_t)rows[b] * dk;
                     }
-                    __syncthreads();
-                    for (int rr = warp; rr < nq * rep; rr += nw) {
-                        const int qi = rr / rep, r = qi * H + c * rep + rr % rep;
-                        const int pq = pos0 + qi;
-                        float s = 0.f;
-                        if (lane < nk) {
-                            const float* qv = sQ + (size_t)r * dk;
-                            const float* kv = sT + lane * ts;
+                    float sc[WA_RB] = {0.f, 0.f, 0.f, 0.f};
+                    if (lane < nk) {
+                        const float* kv = sT + ((size_t)cl_ * WA_KT + lane) * ts;
 #pragma unroll 4
-                            for (int i = 0; i < dk; ++i) s = fmaf(qv[i], kv[i], s);
-                            if (p.cap > 0.f) s = p.cap * tanhf(s / p.cap);
+                        for (int i = 0; i < dk; ++i) {
+                            const float kx = kv[i];
+#pragma unroll
+                            for (int b = 0; b < WA_RB; ++b) sc[b] = fmaf(qv[b][i], kx, sc[b]);
                         }
+                    }
+#pragma unroll
+                    for (int b = 0; b < WA_RB; ++b) {
+                        if (b >= nr) break;
+                        const int r = rows[b], pq = pos0 + r / H;
+                        float s = sc[b];
+                        if (p.cap > 0.f) s = p.cap * tanhf(s / p.cap);
                         const bool vis = lane < nk && jl <= pq && (pq - jl < p.window || jl < p.keep);
                         if (pass == 0) {
                             float mx = vis ? s : -CUDART_INF_F;
@@ -171,44 +208,80 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
                                 __syncwarp();
                             }
                         } else {
-                            sP[r * WA_KT + lane] = vis ? expf(s - sMax[r]) / sSum[r] : 0.f;
+                            sP[r * WA_KT + lane] = vis ? expf(s - sGMax[r]) / sGSum[r] : 0.f;
                         }
                     }
                 }
-                if (pass == 0) continue;
+            }
+            if (pass == 0) continue;
+            __syncthreads();
+            for (int e = threadIdx.x; e < R * WA_KT; e += WA_THREADS) {
+                const int r = e / WA_KT, kt = e % WA_KT, qi = r / H, h = r % H;
+                float a = 0.f;
+                for (int g = 0; g < H; ++g) a = fmaf(sMix[h * H + g], sP[(qi * H + g) * WA_KT + kt], a);
+                sM[e] = a;
+            }
+            for (int c0 = 0; c0 < G; c0 += p.gt) {
+                const int gn = min(p.gt, G - c0);
+                __syncthreads();                   // mixed weights written / the tile buffer is free
+                for (int e = warp; e < gn * nk; e += nw) {
+                    const int cl_ = e / nk, kt = e % nk, j = j0 + kt;
+                    const float* src = p.cache + ((size_t)tbl[j / p.page] * p.page + j % p.page) * D + (size_t)G * dk + (size_t)(c0 + cl_) * dv;
+                    float* dst = sT + ((size_t)cl_ * WA_KT + kt) * ts;
+                    for (int i = lane; i < dv; i += 32) dst[i] = src[i];
+                }
                 __syncthreads();
-                for (int e = threadIdx.x; e < R * WA_KT; e += WA_THREADS) {
-                    const int r = e / WA_KT, kt = e % WA_KT, qi = r / H, h = r % H;
-                    float a = 0.f;
-                    for (int g = 0; g < H; ++g) a = fmaf(sMix[h * H + g], sP[(qi * H + g) * WA_KT + kt], a);
-                    sM[e] = a;
-                }
-                for (int c = 0; c < G; ++c) {
-                    __syncthreads();               // mixed weights written / the tile buffer is free
-                    for (int kt = warp; kt < nk; kt += nw) {
-                        const int j = j0 + kt;
-                        const float* src = p.cache + ((size_t)tbl[j / p.page] * p.page + j % p.page) * D + (size_t)G * dk + (size_t)c * dv;
-                        for (int i = lane; i < dv; i += 32) sT[kt * ts + i] = src[i];
+                for (int it = warp; it < gn * nblk; it += nw) {
+                    const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * WA_RB, nr = min(WA_RB, nrg - rr0);
+                    int rows[WA_RB];
+#pragma unroll
+                    for (int b = 0; b < WA_RB; ++b) {
+                        const int rr = rr0 + min(b, nr - 1);
+                        rows[b] = (rr / rep) * H + c * rep + rr % rep;
                     }
-                    __syncthreads();
-                    for (int rr = warp; rr < nq * rep; rr += nw) {
-                        const int qi = rr / rep, r = qi * H + c * rep + rr % rep;
-                        const float* w = sM + r * WA_KT;
-                        for (int d = lane; d < dv; d += 32) {
-                            float acc = sO[(size_t)r * dv + d];
-                            for (int kt = 0; kt < nk; ++kt) acc = fmaf(w[kt], sT[kt * ts + d], acc);
-                            sO[(size_t)r * dv + d] = acc;
+                    const float* vt = sT + (size_t)cl_ * WA_KT * ts;
+                    for (int d = lane; d < dv; d += 32) {
+                        float acc[WA_RB];
+#pragma unroll
+                        for (int b = 0; b < WA_RB; ++b) acc[b] = sO[(size_t)rows[b] * dv + d];
+                        for (int kt = 0; kt < nk; ++kt) {
+                            const float vx = vt[kt * ts + d];
+#pragma unroll
+                            for (int b = 0; b < WA_RB; ++b) acc[b] = fmaf(sM[rows[b] * WA_KT + kt], vx, acc[b]);
                         }
+#pragma unroll
+                        for (int b = 0; b < WA_RB; ++b)
+                            if (b < nr) sO[(size_t)rows[b] * dv + d] = acc[b];
                     }
                 }
             }
         }
         __syncthreads();
+        if (pass == 0) {
+            // the chunk's maximum and sum of every row: the CTAs' partial results combined in rank order (the same in every CTA)
+            cluster.sync();
+            for (int e = threadIdx.x; e < R; e += WA_THREADS) {
+                float m = -CUDART_INF_F;
+                for (int rk = 0; rk < CL; ++rk) m = fmaxf(m, cluster.map_shared_rank(sMax, rk)[e]);
+                float l = 0.f;
+                for (int rk = 0; rk < CL; ++rk) {
+                    const float mr = cluster.map_shared_rank(sMax, rk)[e];
+                    if (mr > -CUDART_INF_F) l += cluster.map_shared_rank(sSum, rk)[e] * expf(mr - m);
+                }
+                sGMax[e] = m; sGSum[e] = l;
+            }
+            __syncthreads();
+        }
     }
-    for (int e = threadIdx.x; e < R * dv; e += WA_THREADS) {
+    // the CTAs' partial sums added in rank order; every CTA finishes its share of the outputs
+    cluster.sync();
+    for (int e = rank * WA_THREADS + threadIdx.x; e < R * dv; e += CL * WA_THREADS) {
+        float a = 0.f;
+        for (int rk = 0; rk < CL; ++rk) a += cluster.map_shared_rank(sO, rk)[e];
         const int r = e / dv, d = e % dv;
-        p.out[(size_t)(t0 + r / H) * p.ldo + (size_t)(r % H) * dv + d] = sO[e];
+        p.out[(size_t)(t0 + r / H) * p.ldo + (size_t)(r % H) * dv + d] = a;
     }
+    cluster.sync();                                // nobody leaves while its shared memory is still being read
 }
 
 }  // namespace b200

@@ -287,13 +287,10 @@ KX_SIZES = {
 }
 
 
-def kemirax_main(args):
-    """Prefill and decode throughput of the Kemirax family beside an RWKV-7 stack of equal width, depth and vocabulary."""
-    from ai00_server_b200 import capi, runtime, synth
-    peaks, peak_kind = read_peaks()
-    hbm, tf = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
-    B, ctx, plen = args.batch, args.context, args.seq_len
-    rng = np.random.default_rng(7)
+def _family_timer(args, rng):
+    """Prefill (public infer call, host clock, best of 3) and decode (graph-replayed steps, CUDA events) of one loaded model."""
+    from ai00_server_b200 import capi
+    B, ctx = args.batch, args.context
 
     def time_arm(m, vocab, reset):
         slots = list(range(B))
@@ -317,41 +314,57 @@ def kemirax_main(args):
                 "decode_ms_per_step": ms / args.steps, "launches_per_step": launches / args.steps,
                 "ungraphed_step_ms_by_class": {"linear": cls_ms[0], "mixer": cls_ms[1], "norm": cls_ms[2], "other": cls_ms[3]},
                 "launches_by_class": list(cls_n)}
+    return time_arm
 
+
+def _kemirax_arm(args, name, time_arm, hbm, tf, peak_kind):
+    """One JSON record: the four-layer Kemirax stack (latent, borrowed-cache latent, gla, latent; routed experts everywhere)."""
+    from ai00_server_b200 import runtime, synth
+    B, ctx = args.batch, args.context
+    z = KX_SIZES[name]
+    W, V = z["width"], z["vocab"]
+    att = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"], q_rank=z["q_rank"],
+               experts=z["experts"], identity=2, top=z["top"], ff=z["ff"], shared_ff=z["shared_ff"],
+               scaling={"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0})
+    gla = dict(heads=z["heads"], dim=z["dim"], vdim=z["vdim"], experts=z["experts"], identity=2, top=z["top"], ff=z["ff"], shared_ff=z["shared_ff"])
+    layers = [synth.kemirax_layer("latent_attention", **att), synth.kemirax_layer("latent_attention", kv_from=0, **att),
+              synth.kemirax_layer("gla", **gla), synth.kemirax_layer("latent_attention", **att)]
+    cfg, st, _ = synth.make_kemirax(layers, width=W, vocab=V, seed=1, gain=0.5, arrays=False)
+    # algorithmic work: weights one token touches (dense + top experts), weights a decode step streams (dense + the experts
+    # its B x top choices can reach), cache rows every attention layer reads
+    E, top, D = z["experts"], z["top"], z["kv_rank"] + z["rot_dim"]
+    expert = 3 * W * z["ff"]
+    H, dn, dr, dv, rk, rq = z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["kv_rank"], z["q_rank"]
+    lat = rq * W + H * (dn + dr) * rq + H * dn * rk + H * dv * rk + W * H * dv
+    dense = {"latent": lat + D * W, "borrow": lat, "gla": 2 * H * dn * W + 2 * H * dv * W + W * H * dv + 8 * W + H * dn * 8}
+    common = 2 * W * W + (E + 2) * W + 3 * W * z["shared_ff"] + W
+    per_layer_dense = [dense["latent"] + common, dense["borrow"] + common, dense["gla"] + common, dense["latent"] + common]
+    reach = min(E, B * top)
+    active = sum(per_layer_dense) + 4 * top * expert + V * W
+    step_bytes = 2 * (sum(per_layer_dense) + 4 * reach * expert + V * W) + 3 * B * ctx * D * 4
+    attn_flops_tok = 3 * 2 * H * (2 * rk + dr) * ctx / 2           # absorbed form, mean context ctx / 2 during the prompt
+    m = runtime.Model(st, max_batch=B, token_chunk_size=512, config=cfg, kv_tokens=B * (ctx + args.warmup + args.steps + 8))
+    r = time_arm(m, V, m.state.reset)
+    m.close()
+    r.update({"family": "kemirax", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(active),
+              "decode_algorithmic_bytes_per_step": int(step_bytes),
+              "decode_frac_of_hbm_peak": step_bytes / (r["decode_ms_per_step"] * 1e-3) / (hbm * 1e9),
+              "prefill_tflops": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12,
+              "prefill_frac_of_bf16_peak": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12 / tf,
+              "peaks": peak_kind, "dtype": "bf16", "data": "synthetic"})
+    return r
+
+
+def kemirax_main(args):
+    """Prefill and decode throughput of the Kemirax family beside an RWKV-7 stack of equal width, depth and vocabulary."""
+    from ai00_server_b200 import runtime, synth
+    peaks, peak_kind = read_peaks()
+    hbm, tf = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
+    B, ctx = args.batch, args.context
+    time_arm = _family_timer(args, np.random.default_rng(7))
     for name in args.kx_sizes.split(","):
-        z = KX_SIZES[name]
-        W, V = z["width"], z["vocab"]
-        att = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"], q_rank=z["q_rank"],
-                   experts=z["experts"], identity=2, top=z["top"], ff=z["ff"], shared_ff=z["shared_ff"],
-                   scaling={"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0})
-        gla = dict(heads=z["heads"], dim=z["dim"], vdim=z["vdim"], experts=z["experts"], identity=2, top=z["top"], ff=z["ff"], shared_ff=z["shared_ff"])
-        layers = [synth.kemirax_layer("latent_attention", **att), synth.kemirax_layer("latent_attention", kv_from=0, **att),
-                  synth.kemirax_layer("gla", **gla), synth.kemirax_layer("latent_attention", **att)]
-        cfg, st, _ = synth.make_kemirax(layers, width=W, vocab=V, seed=1, gain=0.5, arrays=False)
-        # algorithmic work: weights one token touches (dense + top experts), weights a decode step streams (dense + the experts
-        # its B x top choices can reach), cache rows every attention layer reads
-        E, top, D = z["experts"], z["top"], z["kv_rank"] + z["rot_dim"]
-        expert = 3 * W * z["ff"]
-        H, dn, dr, dv, rk, rq = z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["kv_rank"], z["q_rank"]
-        lat = rq * W + H * (dn + dr) * rq + H * dn * rk + H * dv * rk + W * H * dv
-        dense = {"latent": lat + D * W, "borrow": lat, "gla": 2 * H * dn * W + 2 * H * dv * W + W * H * dv + 8 * W + H * dn * 8}
-        common = 2 * W * W + (E + 2) * W + 3 * W * z["shared_ff"] + W
-        per_layer_dense = [dense["latent"] + common, dense["borrow"] + common, dense["gla"] + common, dense["latent"] + common]
-        reach = min(E, B * top)
-        active = sum(per_layer_dense) + 4 * top * expert + V * W
-        step_bytes = 2 * (sum(per_layer_dense) + 4 * reach * expert + V * W) + 3 * B * ctx * D * 4
-        attn_flops_tok = 3 * 2 * H * (2 * rk + dr) * ctx / 2           # absorbed form, mean context ctx / 2 during the prompt
-        m = runtime.Model(st, max_batch=B, token_chunk_size=512, config=cfg, kv_tokens=B * (ctx + args.warmup + args.steps + 8))
-        r = time_arm(m, V, m.state.reset)
-        m.close()
-        r.update({"family": "kemirax", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(active),
-                  "decode_algorithmic_bytes_per_step": int(step_bytes),
-                  "decode_frac_of_hbm_peak": step_bytes / (r["decode_ms_per_step"] * 1e-3) / (hbm * 1e9),
-                  "prefill_tflops": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12,
-                  "prefill_frac_of_bf16_peak": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12 / tf,
-                  "peaks": peak_kind, "dtype": "bf16", "data": "synthetic"})
-        print(json.dumps(r), flush=True)
-        del st
+        W, V = KX_SIZES[name]["width"], KX_SIZES[name]["vocab"]
+        print(json.dumps(_kemirax_arm(args, name, time_arm, hbm, tf, peak_kind)), flush=True)
         # the closest existing family at equal size: RWKV-7, same width, depth and vocabulary, hidden = 4 x width
         shp = synth.Shape(7, 4, W, 4 * W, V=V, Dd=64, Da=64, Dv=32, Dg=128)
         st7 = synth.make_st(shp, 0)
@@ -368,6 +381,62 @@ def kemirax_main(args):
                    "prefill_frac_of_bf16_peak": 2 * p7 * r7["prefill_tokens_per_s"] / 1e12 / tf,
                    "peaks": peak_kind, "dtype": "fp16", "data": "synthetic"})
         print(json.dumps(r7), flush=True)
+
+
+DG_SIZES = {
+    # width; mixer heads / key-value heads / head sizes; attention window + kept tokens; experts x ff, top, shared ff; dense ff; low ranks; vocab
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, window=512, keep_first=4, conv=4, experts=8, ff=512, top=2, shared_ff=1024,
+                  dense_ff=2816, low_rank=64, vocab=32768),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=512, keep_first=4, conv=4, experts=16, ff=1024, top=4, shared_ff=2048,
+                  dense_ff=5632, low_rank=128, vocab=32768),
+}
+
+
+def degavik_main(args):
+    """Prefill and decode throughput of the Degavik family (retention + dense, delta rule + experts, windowed attention + experts,
+    delta rule + dense) beside the closest existing family, a Kemirax stack of equal width, depth and vocabulary."""
+    from ai00_server_b200 import runtime, synth
+    peaks, peak_kind = read_peaks()
+    hbm, tf = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
+    B, ctx = args.batch, args.context
+    time_arm = _family_timer(args, np.random.default_rng(7))
+    L = synth.degavik_layer
+    for name in args.kx_sizes.split(","):
+        z = DG_SIZES[name]
+        W, V, H, G, dk, dv, E, top, r_ = z["width"], z["vocab"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["experts"], z["top"], z["low_rank"]
+        moe = dict(mlp="moe", experts=E, top=top, ff=z["ff"], shared_ff=z["shared_ff"])
+        dense = dict(mlp="dense", ff=z["dense_ff"])
+        hd = dict(heads=H, dim=dk, vdim=dv)
+        layers = [L("retention", base=1e6, **hd, **dense), L("channel_delta", kv_heads=G, conv=z["conv"], **hd, **moe),
+                  L("attention", kv_heads=G, rot_dims=dk // 2, base=5e5, window=z["window"], keep_first=z["keep_first"], softcap=30.0, **hd, **moe),
+                  L("channel_delta", kv_heads=G, conv=z["conv"], **hd, **dense)]
+        cfg, st, _ = synth.make_degavik(layers, width=W, vocab=V, seed=1, low_rank=r_, arrays=False)
+        # algorithmic work: weights one token touches, weights a decode step streams (dense + reachable experts), recurrent states
+        # read and written, cache rows inside the window
+        o = W * H * dv
+        mix = {"ret": 2 * H * dk * W + 2 * H * dv * W + o,
+               "delta": 2 * G * dk * W + H * dv * W + H * W + 2 * r_ * W + H * dk * r_ + H * dv * r_ + o,
+               "attn": H * dk * W + G * dk * W + G * dv * W + o}
+        ff_moe, ff_dense, expert = E * W + 3 * W * z["shared_ff"], 3 * W * z["dense_ff"], 3 * W * z["ff"]
+        per_layer = [mix["ret"] + ff_dense, mix["delta"] + ff_moe, mix["attn"] + ff_moe, mix["delta"] + ff_dense]
+        reach = min(E, B * top)
+        active = sum(per_layer) + 2 * top * expert + V * W
+        seen = min(ctx, z["window"] + z["keep_first"])
+        state_bytes = 3 * B * H * dk * dv * 4 * 2                       # three recurrent layers, read + write
+        step_bytes = 2 * (sum(per_layer) + 2 * reach * expert + V * W) + state_bytes + B * seen * G * (dk + dv) * 4
+        attn_flops_tok = 2 * H * (dk + dv) * min(ctx / 2, seen) + 3 * 2 * 2 * H * dk * dv       # scores + values, three state updates
+        m = runtime.Model(st, max_batch=B, token_chunk_size=512, config=cfg, kv_tokens=B * (ctx + args.warmup + args.steps + 8))
+        r = time_arm(m, V, m.state.reset)
+        m.close()
+        r.update({"family": "degavik", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(active),
+                  "decode_algorithmic_bytes_per_step": int(step_bytes),
+                  "decode_frac_of_hbm_peak": step_bytes / (r["decode_ms_per_step"] * 1e-3) / (hbm * 1e9),
+                  "prefill_tflops": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12,
+                  "prefill_frac_of_bf16_peak": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12 / tf,
+                  "peaks": peak_kind, "dtype": "bf16", "data": "synthetic"})
+        print(json.dumps(r), flush=True)
+        del st
+        print(json.dumps(_kemirax_arm(args, name, time_arm, hbm, tf, peak_kind)), flush=True)
 
 
 def main():
@@ -388,15 +457,19 @@ def main():
     ap.add_argument("--quant-layers", type=int, default=-1, help="the reference's `quant`: first N layers (default: all)")
     ap.add_argument("--seqs", type=int, default=256)
     ap.add_argument("--seq-len", type=int, default=512)
-    ap.add_argument("--family", default="rwkv", choices=["rwkv", "kemirax"],
-                    help="kemirax: prefill and decode throughput of the Kemirax family at layer sizes of a real model (random weights), "
-                         "beside an RWKV-7 stack of equal width and depth; one JSON line per arm (not the headline workload)")
-    ap.add_argument("--kx-sizes", default="w1024,w2048", help="--family kemirax: comma-separated size names")
-    ap.add_argument("--context", type=int, default=1024, help="--family kemirax: tokens each sequence holds before the timed decode steps")
+    ap.add_argument("--family", default="rwkv", choices=["rwkv", "kemirax", "degavik"],
+                    help="kemirax / degavik: prefill and decode throughput of that family at layer sizes of a real model (random weights), "
+                         "beside the closest existing family at equal width and depth (RWKV-7 for kemirax, Kemirax for degavik); one "
+                         "JSON line per arm (not the headline workload)")
+    ap.add_argument("--kx-sizes", default="w1024,w2048", help="--family kemirax / degavik: comma-separated size names")
+    ap.add_argument("--context", type=int, default=1024,
+                    help="--family kemirax / degavik: tokens each sequence holds before the timed decode steps")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.family == "kemirax":
         return kemirax_main(args)
+    if args.family == "degavik":
+        return degavik_main(args)
     PRESET, BATCH = args.preset, args.batch
     METRIC = metric_name(PRESET, BATCH)
     if args.quant != "none":
