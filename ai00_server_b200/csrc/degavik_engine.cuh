@@ -189,7 +189,12 @@ void b200rwkv_engine::dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int
     if (c.mixer == KX_RETENTION) {
         RetentionParams rp{m.pr, m.pr + H_ * dk, m.pr + 2 * H_ * dk, m.pr + 2 * H_ * dk + H_ * dv, PN, l.rec_state, m.vout, H_ * dv, l.decay, l.freq_d,
                            H_, dk, dv, c.rot.dims, 1.f / sqrtf((float)dk), m.cfg.eps, mv, m.sm};
-        launch_k(retention_kernel, dim3(H_, nslot_grid), dim3(rup(dv, 32)), retention_smem_bytes(dk, dv), rp, KC_WKV, s, prof);
+        if (dk <= RET_REG_MAX_DK && dv <= RET_REG_MAX_DV) {       // usual head sizes: the state column lives in registers
+            auto kern = dk <= 32 ? retention_reg_kernel<32> : (dk <= 64 ? retention_reg_kernel<64> : retention_reg_kernel<128>);
+            launch_k(kern, dim3(H_, nslot_grid), dim3(rup(dv, 32)), 0, rp, KC_WKV, s, prof);
+        } else {
+            launch_k(retention_kernel, dim3(H_, nslot_grid), dim3(rup(dv, 32)), retention_smem_bytes(dk, dv), rp, KC_WKV, s, prof);
+        }
     } else if (c.mixer == KX_DELTA) {
         const int C_ = l.conv_C;
         ShortConvParams cp{m.pr, PN, m.cv, C_, l.conv_w, l.conv_tail, C_, c.taps, mv};
@@ -199,7 +204,12 @@ void b200rwkv_engine::dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int
         kx_lin(s, prof, lin(m.pr + C_ + H_ + l.a_rank, PN, l.g2, m.gl, H_ * dv, H_ * dv, l.g_rank), rows, 1);
         DeltaRuleParams dp{m.cv, m.cv + G_ * dk, m.cv + 2 * G_ * dk, C_, m.z, H_ * dk, m.pr + C_, PN, m.gl, H_ * dv, l.a_log, l.norm_w, l.rec_state,
                            m.vout, H_ * dv, H_, G_, dk, dv, 1.f / sqrtf((float)dk), 1e-6f, m.cfg.eps, mv};
-        launch_k(delta_rule_kernel, dim3(H_, nslot_grid), dim3(rup(dv, 32)), delta_rule_smem_bytes(dk, dv), dp, KC_WKV, s, prof);
+        if (dk <= DR_REG_MAX_DK && dv <= DR_REG_MAX_DV) {
+            auto kern = dk <= 32 ? delta_rule_reg_kernel<32> : (dk <= 64 ? delta_rule_reg_kernel<64> : delta_rule_reg_kernel<128>);
+            launch_k(kern, dim3(H_, nslot_grid), dim3(rup(dv, 32)), 0, dp, KC_WKV, s, prof);
+        } else {
+            launch_k(delta_rule_kernel, dim3(H_, nslot_grid), dim3(rup(dv, 32)), delta_rule_smem_bytes(dk, dv), dp, KC_WKV, s, prof);
+        }
     } else {
         AttnPrepParams ap{m.pr, m.pr + H_ * dk, m.pr + H_ * dk + G_ * dk, PN, m.q, H_ * dk, l.cache, m.d_table, m.npages, m.page, l.qn_w, l.kn_w,
                           l.temp, l.freq_d, H_, G_, dk, dv, c.rot.dims, c.scale, m.cfg.eps, mv, m.sm};

@@ -12,6 +12,7 @@
 //                         (the last taps - 1 inputs, zeros at the start of a sequence)
 //   conv_commit_kernel    the step's last taps - 1 inputs become the sequence's new tail rows (own launch: every token of the
 //                         step has read the old tail by then)
+//   delta_rule_reg_kernel the state column of thread j in registers (dk <= 128, dv <= 256): the form that runs for usual head sizes
 //   delta_rule_kernel     one CTA per (value head, sequence of the step): the state sits in shared memory for the sequence's
 //                         tokens of this step, column j belongs to thread j (two passes over the column per token: decay +
 //                         S^T k, then update + read-out; no cross-thread traffic besides the unit norms and the output norm)
@@ -164,6 +165,88 @@ __global__ void delta_rule_kernel(const DeltaRuleParams p) {
         for (int e = j; e < nst / 4; e += blockDim.x) reinterpret_cast<float4*>(gS)[e] = reinterpret_cast<const float4*>(S)[e];
     } else {
         for (int e = j; e < nst; e += blockDim.x) gS[e] = S[e];
+    }
+}
+
+// The same recurrence with the state column in REGISTERS (dk <= DKC <= 128, dv <= 256): thread j keeps S[0..dk)[j] for the whole
+// step, so the two passes over the column are straight-line FMAs on registers fed by broadcast reads of q, k and g from shared
+// memory (the shared-memory form above pays a load-after-store round trip per element).  Four partial sums shorten the
+// dependency chains of the two dot products.
+constexpr int DR_REG_MAX_DK = 128, DR_REG_MAX_DV = 256;
+
+template <int DKC>
+__global__ void __launch_bounds__(DR_REG_MAX_DV) delta_rule_reg_kernel(const DeltaRuleParams p) {
+    const int h = blockIdx.x, si = blockIdx.y;
+    if (si >= p.meta.nslots()) return;
+    const int slot = p.meta.slot_id()[si], t0 = p.meta.slot_start()[si], nt = p.meta.slot_count()[si];
+    const int dk = p.dk, dv = p.dv, j = threadIdx.x, hk = h / (p.H / p.G);
+    const int nw = (blockDim.x + 31) >> 5;
+    __shared__ __align__(16) float sq[DKC], sk[DKC], sg[DKC];
+    __shared__ float red[64];
+    float* gS = p.state + ((size_t)slot * p.H + h) * dk * dv;
+    float s[DKC];
+#pragma unroll
+    for (int i = 0; i < DKC; ++i) s[i] = (i < dk && j < dv) ? gS[(size_t)i * dv + j] : 0.f;
+    const float rate = expf(p.a_log[h]);
+    for (int t = t0; t < t0 + nt; ++t) {
+        __syncthreads();
+        float qq = 0.f, kk = 0.f;
+        for (int i = j; i < DKC; i += blockDim.x) {
+            float qv = 0.f, kv = 0.f, gv = 1.f;
+            if (i < dk) {
+                qv = p.q[(size_t)t * p.ld + (size_t)hk * dk + i]; kv = p.k[(size_t)t * p.ld + (size_t)hk * dk + i];
+                const float zz = p.z[(size_t)t * p.ldz + (size_t)h * dk + i];
+                gv = expf(-rate * (fmaxf(zz, 0.f) + log1pf(expf(-fabsf(zz)))));
+            }
+            sq[i] = qv; sk[i] = kv; sg[i] = gv;
+            qq = fmaf(qv, qv, qq); kk = fmaf(kv, kv, kk);
+        }
+#pragma unroll
+        for (int of = 16; of > 0; of >>= 1) { qq += __shfl_xor_sync(0xffffffffu, qq, of); kk += __shfl_xor_sync(0xffffffffu, kk, of); }
+        if ((j & 31) == 0) { red[j >> 5] = qq; red[32 + (j >> 5)] = kk; }
+        __syncthreads();
+        qq = 0.f; kk = 0.f;
+        for (int w = 0; w < nw; ++w) { qq += red[w]; kk += red[32 + w]; }
+        const float qn = p.q_scale / sqrtf(qq + p.unit_eps), kn = 1.f / sqrtf(kk + p.unit_eps);
+        const float beta = 1.f / (1.f + expf(-p.b[(size_t)t * p.ldb + h]));
+        float o = 0.f;
+        if (j < dv) {
+            const float vj = p.v[(size_t)t * p.ld + (size_t)h * dv + j];
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DKC; i += 4) {
+                s[i] *= sg[i]; s[i + 1] *= sg[i + 1]; s[i + 2] *= sg[i + 2]; s[i + 3] *= sg[i + 3];
+                d0 = fmaf(s[i], sk[i], d0); d1 = fmaf(s[i + 1], sk[i + 1], d1);
+                d2 = fmaf(s[i + 2], sk[i + 2], d2); d3 = fmaf(s[i + 3], sk[i + 3], d3);
+            }
+            const float u = beta * (vj - ((d0 + d1) + (d2 + d3)) * kn) * kn;       // u * kn: the write is k_unit u^T
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DKC; i += 4) {
+                s[i] = fmaf(sk[i], u, s[i]); s[i + 1] = fmaf(sk[i + 1], u, s[i + 1]);
+                s[i + 2] = fmaf(sk[i + 2], u, s[i + 2]); s[i + 3] = fmaf(sk[i + 3], u, s[i + 3]);
+                o0 = fmaf(s[i], sq[i], o0); o1 = fmaf(s[i + 1], sq[i + 1], o1);
+                o2 = fmaf(s[i + 2], sq[i + 2], o2); o3 = fmaf(s[i + 3], sq[i + 3], o3);
+            }
+            o = ((o0 + o1) + (o2 + o3)) * qn;
+        }
+        float ss = j < dv ? o * o : 0.f;
+#pragma unroll
+        for (int of = 16; of > 0; of >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, of);
+        __syncthreads();                           // red has been read by every thread
+        if ((j & 31) == 0) red[j >> 5] = ss;
+        __syncthreads();
+        ss = 0.f;
+        for (int w = 0; w < nw; ++w) ss += red[w];
+        if (j < dv) {
+            const float gl = p.gate[(size_t)t * p.ldgate + (size_t)h * dv + j];
+            p.out[(size_t)t * p.ldo + (size_t)h * dv + j] = o / sqrtf(ss / (float)dv + p.eps) * p.norm_w[j] * (1.f / (1.f + expf(-gl)));
+        }
+    }
+    if (j < dv) {
+#pragma unroll
+        for (int i = 0; i < DKC; ++i)
+            if (i < dk) gS[(size_t)i * dv + j] = s[i];
     }
 }
 

@@ -25,6 +25,7 @@
 #include <math_constants.h>
 #include "common.cuh"
 #include "latent_attn.cuh"
+#include "linear.cuh"
 
 namespace b200 {
 
@@ -100,7 +101,33 @@ constexpr int WA_RB = 4;                           // rows of one key / value he
 
 __host__ __device__ inline size_t window_attn_smem(int qb, int H, int dk, int dv, int gt) {
     const size_t R = (size_t)qb * H, dmax = dk > dv ? dk : dv;
-    return (R * dk + R * dv + 2 * R * WA_KT + (size_t)gt * WA_KT * (dmax + 1) + 4 * R + (size_t)H * H + 8) * sizeof(float);
+    return (R * dk + R * dv + 2 * R * WA_KT + (size_t)gt * WA_KT * (dmax + 4) + 4 * R + (size_t)H * H + 8) * sizeof(float);
+}
+
+// `nk` cache rows from position j0 on, `w` floats at offset `off` of each of `gn` consecutive heads -> tile[head][key][ts].  vec:
+// 16-byte cp.async copies issued by all threads at once (every row address comes from the page table first, so the copies of a
+// tile are in flight together); otherwise plain loads.  Ends with the data visible to the whole CTA.
+__device__ __forceinline__ void wa_load_tile(const float* cache, const int* tbl, int page, int D, size_t off, int w, float* tile, int ts, int gn,
+                                             int nk, int j0, bool vec) {
+    if (vec) {
+        const int w4 = w >> 2, total = gn * nk * w4;
+        for (int e = threadIdx.x; e < total; e += WA_THREADS) {
+            const int row = e / w4, v4 = e % w4, cl_ = row / nk, kt = row % nk, j = j0 + kt;
+            const float* src = cache + ((size_t)tbl[j / page] * page + j % page) * D + off + (size_t)cl_ * w + (size_t)v4 * 4;
+            cp_async16(tile + ((size_t)cl_ * WA_KT + kt) * ts + v4 * 4, src);
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    } else {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int e = warp; e < gn * nk; e += WA_THREADS / 32) {
+            const int cl_ = e / nk, kt = e % nk, j = j0 + kt;
+            const float* src = cache + ((size_t)tbl[j / page] * page + j % page) * D + off + (size_t)cl_ * w;
+            float* dst = tile + ((size_t)cl_ * WA_KT + kt) * ts;
+            for (int i = lane; i < w; i += 32) dst[i] = src[i];
+        }
+    }
+    __syncthreads();
 }
 
 // the tile `ti` of the key walk: segment 0 first, then segment 1
@@ -119,7 +146,11 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
     const int slot = p.meta.tok_slot()[t0];
     const int pos0 = p.sm.tok_pos()[t0], pos1 = pos0 + nq - 1;
     const int H = p.H, G = p.G, dk = p.dk, dv = p.dv, rep = H / G, R = nq * H;
-    const int dmax = dk > dv ? dk : dv, ts = dmax + 1, D = G * (dk + dv);
+    // head sizes that are multiples of four: rows of the tile buffer start on 16 bytes (stride dmax + 4: a quarter warp's 16-byte
+    // reads of eight different rows fall into different banks), tiles arrive by cp.async and the score loop reads four floats at
+    // a time; otherwise stride dmax + 1 and scalar loads
+    const bool vec = (dk % 4 == 0) && (dv % 4 == 0);
+    const int dmax = dk > dv ? dk : dv, ts = dmax + (vec ? 4 : 1), D = G * (dk + dv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = WA_THREADS / 32;
     extern __shared__ __align__(16) float wa_smem[];
     const int Rcap = p.qb * H;
@@ -161,13 +192,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
             for (int c0 = 0; c0 < G; c0 += p.gt) {
                 const int gn = min(p.gt, G - c0);
                 __syncthreads();                   // the tile buffer is free
-                for (int e = warp; e < gn * nk; e += nw) {
-                    const int cl_ = e / nk, kt = e % nk, j = j0 + kt;
-                    const float* src = p.cache + ((size_t)tbl[j / p.page] * p.page + j % p.page) * D + (size_t)(c0 + cl_) * dk;
-                    float* dst = sT + ((size_t)cl_ * WA_KT + kt) * ts;
-                    for (int i = lane; i < dk; i += 32) dst[i] = src[i];
-                }
-                __syncthreads();
+                wa_load_tile(p.cache, tbl, p.page, D, (size_t)c0 * dk, dk, sT, ts, gn, nk, j0, vec);
                 for (int it = warp; it < gn * nblk; it += nw) {
                     const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * WA_RB, nr = min(WA_RB, nrg - rr0);
                     int rows[WA_RB];
@@ -181,11 +206,25 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
                     float sc[WA_RB] = {0.f, 0.f, 0.f, 0.f};
                     if (lane < nk) {
                         const float* kv = sT + ((size_t)cl_ * WA_KT + lane) * ts;
-#pragma unroll 4
-                        for (int i = 0; i < dk; ++i) {
-                            const float kx = kv[i];
+                        if (vec) {
+                            const float4* k4 = reinterpret_cast<const float4*>(kv);
+#pragma unroll 2
+                            for (int i = 0; i < dk / 4; ++i) {
+                                const float4 kx = k4[i];
 #pragma unroll
-                            for (int b = 0; b < WA_RB; ++b) sc[b] = fmaf(qv[b][i], kx, sc[b]);
+                                for (int b = 0; b < WA_RB; ++b) {
+                                    const float4 qx = reinterpret_cast<const float4*>(qv[b])[i];
+                                    sc[b] = fmaf(qx.x, kx.x, sc[b]); sc[b] = fmaf(qx.y, kx.y, sc[b]);
+                                    sc[b] = fmaf(qx.z, kx.z, sc[b]); sc[b] = fmaf(qx.w, kx.w, sc[b]);
+                                }
+                            }
+                        } else {
+#pragma unroll 4
+                            for (int i = 0; i < dk; ++i) {
+                                const float kx = kv[i];
+#pragma unroll
+                                for (int b = 0; b < WA_RB; ++b) sc[b] = fmaf(qv[b][i], kx, sc[b]);
+                            }
                         }
                     }
 #pragma unroll
@@ -224,13 +263,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
             for (int c0 = 0; c0 < G; c0 += p.gt) {
                 const int gn = min(p.gt, G - c0);
                 __syncthreads();                   // mixed weights written / the tile buffer is free
-                for (int e = warp; e < gn * nk; e += nw) {
-                    const int cl_ = e / nk, kt = e % nk, j = j0 + kt;
-                    const float* src = p.cache + ((size_t)tbl[j / p.page] * p.page + j % p.page) * D + (size_t)G * dk + (size_t)(c0 + cl_) * dv;
-                    float* dst = sT + ((size_t)cl_ * WA_KT + kt) * ts;
-                    for (int i = lane; i < dv; i += 32) dst[i] = src[i];
-                }
-                __syncthreads();
+                wa_load_tile(p.cache, tbl, p.page, D, (size_t)G * dk + (size_t)c0 * dv, dv, sT, ts, gn, nk, j0, vec);
                 for (int it = warp; it < gn * nblk; it += nw) {
                     const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * WA_RB, nr = min(WA_RB, nrg - rr0);
                     int rows[WA_RB];
