@@ -218,7 +218,9 @@ void b200rwkv_engine::dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int
         WindowAttnParams wp{m.q, H_ * dk, l.cache, m.d_table, m.npages, m.page, m.vout, H_ * dv, l.talk, H_, G_, dk, dv, c.window, c.keep_first,
                             c.softcap, qb, l.wa_gt, nsplit, mv, m.sm};
         launch_cluster = nsplit;
-        launch_k(window_attn_kernel, dim3((decode ? rows : cdiv(rows, qb) + nslot_grid) * nsplit), dim3(WA_THREADS),
+        // 16 warps where the score / value phases have a work item (four rows of one key head) for each, 8 otherwise
+        const int items = std::min(l.wa_gt, G_) * cdiv(qb * (H_ / G_), WA_RB);
+        launch_k(window_attn_kernel, dim3((decode ? rows : cdiv(rows, qb) + nslot_grid) * nsplit), dim3(items >= 16 ? WA_THREADS : 256),
                  window_attn_smem(qb, H_, dk, dv, l.wa_gt), wp, KC_WKV, s, prof);
     }
     kx_lin(s, prof, lin(m.vout, H_ * dv, l.o, m.y, W, W, H_ * dv), rows, 1);

@@ -96,8 +96,8 @@ struct WindowAttnParams {
 };
 
 constexpr int WA_KT = 32;                          // keys per tile (one per lane in the score phase)
-constexpr int WA_THREADS = 256;
-constexpr int WA_RB = 4;                           // rows of one key / value head a warp works on together
+constexpr int WA_THREADS = 512;                     // most threads per CTA; the host launches 256 where fewer warps find work
+constexpr int WA_RB = 4;                           // most rows of one key / value head a warp works on together
 
 __host__ __device__ inline size_t window_attn_smem(int qb, int H, int dk, int dv, int gt) {
     const size_t R = (size_t)qb * H, dmax = dk > dv ? dk : dv;
@@ -110,17 +110,19 @@ __host__ __device__ inline size_t window_attn_smem(int qb, int H, int dk, int dv
 __device__ __forceinline__ void wa_load_tile(const float* cache, const int* tbl, int page, int D, size_t off, int w, float* tile, int ts, int gn,
                                              int nk, int j0, bool vec) {
     if (vec) {
-        const int w4 = w >> 2, total = gn * nk * w4;
-        for (int e = threadIdx.x; e < total; e += WA_THREADS) {
-            const int row = e / w4, v4 = e % w4, cl_ = row / nk, kt = row % nk, j = j0 + kt;
-            const float* src = cache + ((size_t)tbl[j / page] * page + j % page) * D + off + (size_t)cl_ * w + (size_t)v4 * 4;
-            cp_async16(tile + ((size_t)cl_ * WA_KT + kt) * ts + v4 * 4, src);
+        const int w4 = w >> 2, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int kt = warp; kt < nk; kt += (int)(blockDim.x >> 5)) {      // a warp per cache row: one page lookup, then 16 bytes per lane
+            const int j = j0 + kt, pg = j / page;
+            const float* src = cache + ((size_t)tbl[pg] * page + (j - pg * page)) * D + off;
+            float* dst = tile + (size_t)kt * ts;
+            for (int cl_ = 0; cl_ < gn; ++cl_)
+                for (int v4 = lane; v4 < w4; v4 += 32) cp_async16(dst + (size_t)cl_ * WA_KT * ts + v4 * 4, src + (size_t)cl_ * w + v4 * 4);
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     } else {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        for (int e = warp; e < gn * nk; e += WA_THREADS / 32) {
+        for (int e = warp; e < gn * nk; e += (int)(blockDim.x >> 5)) {
             const int cl_ = e / nk, kt = e % nk, j = j0 + kt;
             const float* src = cache + ((size_t)tbl[j / page] * page + j % page) * D + off + (size_t)cl_ * w;
             float* dst = tile + ((size_t)cl_ * WA_KT + kt) * ts;
@@ -151,7 +153,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
     // a time; otherwise stride dmax + 1 and scalar loads
     const bool vec = (dk % 4 == 0) && (dv % 4 == 0);
     const int dmax = dk > dv ? dk : dv, ts = dmax + (vec ? 4 : 1), D = G * (dk + dv);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = WA_THREADS / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     extern __shared__ __align__(16) float wa_smem[];
     const int Rcap = p.qb * H;
     float* sQ = wa_smem;                          // [R][dk]
@@ -164,13 +166,13 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
     float* sGMax = sSum + Rcap;                   // [R] the chunk's (all CTAs of the cluster)
     float* sGSum = sGMax + Rcap;
     float* sMix = sGSum + Rcap;                   // [H][H]
-    for (int e = threadIdx.x; e < R * dk; e += WA_THREADS) {
+    for (int e = threadIdx.x; e < R * dk; e += (int)blockDim.x) {
         const int r = e / dk, i = e % dk;
         sQ[e] = p.q[(size_t)(t0 + r / H) * p.ldq + (size_t)(r % H) * dk + i];
     }
-    for (int e = threadIdx.x; e < R * dv; e += WA_THREADS) sO[e] = 0.f;
-    for (int e = threadIdx.x; e < R; e += WA_THREADS) { sMax[e] = -CUDART_INF_F; sSum[e] = 0.f; }
-    for (int e = threadIdx.x; e < H * H; e += WA_THREADS) sMix[e] = p.mix[e];
+    for (int e = threadIdx.x; e < R * dv; e += (int)blockDim.x) sO[e] = 0.f;
+    for (int e = threadIdx.x; e < R; e += (int)blockDim.x) { sMax[e] = -CUDART_INF_F; sSum[e] = 0.f; }
+    for (int e = threadIdx.x; e < H * H; e += (int)blockDim.x) sMix[e] = p.mix[e];
     // key ranges: the kept prefix [0, a_hi) and the window [b_lo, pos1]; one range when they touch
     int seg_lo[2] = {0, 0}, seg_hi[2] = {0, 0};
     {
@@ -182,7 +184,8 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
     const int n0 = (seg_hi[0] - seg_lo[0] + WA_KT - 1) / WA_KT, ntiles = n0 + (seg_hi[1] - seg_lo[1] + WA_KT - 1) / WA_KT;
     const int* tbl = p.table + (size_t)slot * p.stride;
     const int nrg = nq * rep;                      // rows of one key / value head
-    const int nblk = (nrg + WA_RB - 1) / WA_RB;    // row blocks of one head
+    const int rb = WA_RB;                          // rows a warp takes together: they share every key / value operand
+    const int nblk = (nrg + rb - 1) / rb;          // row blocks of one head
     __syncthreads();
     for (int pass = 0; pass < 2; ++pass) {
         for (int ti = rank; ti < ntiles; ti += CL) {
@@ -194,7 +197,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
                 __syncthreads();                   // the tile buffer is free
                 wa_load_tile(p.cache, tbl, p.page, D, (size_t)c0 * dk, dk, sT, ts, gn, nk, j0, vec);
                 for (int it = warp; it < gn * nblk; it += nw) {
-                    const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * WA_RB, nr = min(WA_RB, nrg - rr0);
+                    const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * rb, nr = min(rb, nrg - rr0);
                     int rows[WA_RB];
                     const float* qv[WA_RB];
 #pragma unroll
@@ -208,7 +211,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
                         const float* kv = sT + ((size_t)cl_ * WA_KT + lane) * ts;
                         if (vec) {
                             const float4* k4 = reinterpret_cast<const float4*>(kv);
-#pragma unroll 2
+#pragma unroll 4
                             for (int i = 0; i < dk / 4; ++i) {
                                 const float4 kx = k4[i];
 #pragma unroll
@@ -254,7 +257,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
             }
             if (pass == 0) continue;
             __syncthreads();
-            for (int e = threadIdx.x; e < R * WA_KT; e += WA_THREADS) {
+            for (int e = threadIdx.x; e < R * WA_KT; e += (int)blockDim.x) {
                 const int r = e / WA_KT, kt = e % WA_KT, qi = r / H, h = r % H;
                 float a = 0.f;
                 for (int g = 0; g < H; ++g) a = fmaf(sMix[h * H + g], sP[(qi * H + g) * WA_KT + kt], a);
@@ -265,7 +268,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
                 __syncthreads();                   // mixed weights written / the tile buffer is free
                 wa_load_tile(p.cache, tbl, p.page, D, (size_t)G * dk + (size_t)c0 * dv, dv, sT, ts, gn, nk, j0, vec);
                 for (int it = warp; it < gn * nblk; it += nw) {
-                    const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * WA_RB, nr = min(WA_RB, nrg - rr0);
+                    const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * rb, nr = min(rb, nrg - rr0);
                     int rows[WA_RB];
 #pragma unroll
                     for (int b = 0; b < WA_RB; ++b) {
@@ -277,6 +280,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
                         float acc[WA_RB];
 #pragma unroll
                         for (int b = 0; b < WA_RB; ++b) acc[b] = sO[(size_t)rows[b] * dv + d];
+#pragma unroll 4
                         for (int kt = 0; kt < nk; ++kt) {
                             const float vx = vt[kt * ts + d];
 #pragma unroll
@@ -293,7 +297,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
         if (pass == 0) {
             // the chunk's maximum and sum of every row: the CTAs' partial results combined in rank order (the same in every CTA)
             cluster.sync();
-            for (int e = threadIdx.x; e < R; e += WA_THREADS) {
+            for (int e = threadIdx.x; e < R; e += (int)blockDim.x) {
                 float m = -CUDART_INF_F;
                 for (int rk = 0; rk < CL; ++rk) m = fmaxf(m, cluster.map_shared_rank(sMax, rk)[e]);
                 float l = 0.f;
@@ -308,7 +312,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const WindowAtt
     }
     // the CTAs' partial sums added in rank order; every CTA finishes its share of the outputs
     cluster.sync();
-    for (int e = rank * WA_THREADS + threadIdx.x; e < R * dv; e += CL * WA_THREADS) {
+    for (int e = rank * (int)blockDim.x + threadIdx.x; e < R * dv; e += CL * (int)blockDim.x) {
         float a = 0.f;
         for (int rk = 0; rk < CL; ++rk) a += cluster.map_shared_rank(sO, rk)[e];
         const int r = e / dv, d = e % dv;
