@@ -76,11 +76,16 @@ static KxConfig dg_parse_config(const JVal& root) {
         c.layers.push_back(k);
     }
     const int nl = (int)c.layers.size();
-    for (int i = 0; i < nl; ++i) {
-        const int j = c.layers[i].weights_of;
-        if (j < 0) continue;
-        REQUIRE(j < nl && j != i && c.layers[j].weights_of < 0, B200RWKV_ERR_INVALID, "config: weights_of must name a layer that has tensors of its own");
+    for (int i = 0; i < nl; ++i) {              // a named layer that itself names another: follow to the layer that owns the tensors
+        int j = c.layers[i].weights_of;
+        for (int hops = 0; j >= 0 && j < nl && c.layers[j].weights_of >= 0; ++hops) {
+            REQUIRE(hops < nl, B200RWKV_ERR_INVALID, "config: weights_of forms a cycle");
+            j = c.layers[j].weights_of;
+        }
+        if (c.layers[i].weights_of < 0) continue;
+        REQUIRE(j >= 0 && j < nl && j != i, B200RWKV_ERR_INVALID, "config: weights_of must name a layer that has tensors of its own");
         REQUIRE(c.layers[j].mixer == c.layers[i].mixer, B200RWKV_ERR_INVALID, "config: weights_of names a layer of another type");
+        c.layers[i].weights_of = j;
     }
     return c;
 }

@@ -166,6 +166,26 @@ void b200rwkv_engine::dg_load(const StFile& st, KxSizes& z) {
     CK(cudaFuncSetAttribute(retention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     CK(cudaFuncSetAttribute(delta_rule_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     CK(cudaFuncSetAttribute(window_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    // the largest cluster the attention launch may ask for: what the device can co-schedule at this layer's shared memory
+    m.max_split = 8;
+    for (const KxLayer& l : m.layers) {
+        if (l.c.mixer != KX_WINDOW) continue;
+        int cl = 8;
+        for (; cl > 1; cl >>= 1) {
+            cudaLaunchConfig_t cfg;
+            memset(&cfg, 0, sizeof(cfg));
+            cfg.gridDim = dim3(cl); cfg.blockDim = dim3(WA_THREADS);
+            cfg.dynamicSmemBytes = window_attn_smem(qb, l.c.heads, l.c.dim, l.c.vdim, l.wa_gt);
+            cudaLaunchAttribute at;
+            at.id = cudaLaunchAttributeClusterDimension;
+            at.val.clusterDim.x = (unsigned)cl; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+            cfg.attrs = &at; cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, window_attn_kernel, &cfg) == cudaSuccess && n > 0) break;
+            cudaGetLastError();
+        }
+        m.max_split = std::min(m.max_split, cl);
+    }
     REQUIRE((size_t)W * 4 <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "width too large for the output-norm kernel");
     CK(cudaFuncSetAttribute(norm_add_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
 }

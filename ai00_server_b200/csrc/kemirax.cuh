@@ -259,7 +259,7 @@ struct KxLayer {
 // largest per-token widths of the activation buffers over the layers of a model (filled by the family's loader)
 struct KxSizes {
     size_t n_cq = 1, n_q = 1, n_qa = 1, n_kv = 1, n_part = 1, n_olat = 1, n_vout = 1, n_pr = 1, n_z = 1, n_rl = 1, n_yc = 1, n_ys = 1,
-           n_cv = 1, n_gl = 1, n_bl = 1;
+           n_cv = 1, n_gl = 1;
     int max_top = 1, max_E = 1;
 };
 
@@ -271,7 +271,7 @@ struct Kemirax {
     float final_gain = 1.f;
     float* final_w = nullptr;                     // weight vector of the last norm (families that have one)
     int qb_prompt = 4;                            // tokens per attention chunk of a prompt step
-    float *y = nullptr, *cv = nullptr, *gl = nullptr, *bl = nullptr;   // sublayer output, convolution output, gate / strength logits
+    float *y = nullptr, *cv = nullptr, *gl = nullptr;   // sublayer output, convolution output, output-gate logits
     __nv_bfloat16 *embed = nullptr, *head = nullptr;
     // sequence memory
     int* d_table = nullptr;                       // [S][npages]

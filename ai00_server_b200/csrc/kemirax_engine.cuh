@@ -236,7 +236,7 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
     m.olat = fa(T_ * z.n_olat); m.vout = fa(T_ * z.n_vout); m.pr = fa(T_ * z.n_pr); m.z = fa(T_ * z.n_z);
     m.rl = fa(T_ * z.n_rl); m.wgt = fa(T_ * z.max_top); m.yc = fa(T_ * z.max_top * z.n_yc); m.dn = fa(T_ * z.max_top * W);
     m.ys = fa(T_ * z.n_ys); m.ds = fa(T_ * W);
-    m.y = fa(T_ * W); m.cv = fa(T_ * z.n_cv); m.gl = fa(T_ * z.n_gl); m.bl = fa(T_ * z.n_bl);
+    m.y = fa(T_ * W); m.cv = fa(T_ * z.n_cv); m.gl = fa(T_ * z.n_gl);
     m.lin_ws_floats = (size_t)4 << 20;                   // split-k partial sums of one projection launch
     m.lin_ws = fa(m.lin_ws_floats);
     m.sel = (int*)dalloc(T_ * z.max_top * 4); m.row_of = (int*)dalloc(T_ * z.max_top * 4); m.list = (int*)dalloc(T_ * z.max_top * 4);
@@ -484,7 +484,7 @@ void b200rwkv_engine::kx_fill_step(int* hm, const std::vector<int>& slots, const
             if (l.c.mixer == KX_WINDOW) seen = std::max(seen, std::min(ctx_max, l.c.window + l.c.keep_first + QB));
         const int tiles = cdiv(seen, WA_KT);
         ns = 1;
-        while (ns < 8 && std::max(1, nch) * ns < num_sms && tiles / (ns * 2) >= 1) ns *= 2;
+        while (ns < m.max_split && std::max(1, nch) * ns < num_sms && tiles / (ns * 2) >= 1) ns *= 2;
     }
     *decode = dec; *nsplit = ns;
 }
