@@ -6,7 +6,7 @@
 using namespace b200;
 
 void b200rwkv_engine::dg_load(const StFile& st, KxSizes& z) {
-    Kemirax& m = *kx;
+    SeqModel& m = *kx;
     const int W = m.W, nl = (int)m.cfg.layers.size();
     m.embed = kx_up16(kx_host_bf16(st, "embed", m.V, W));
     m.head = kx_up16(kx_host_bf16(st, "head", m.V, W));
@@ -192,7 +192,7 @@ void b200rwkv_engine::dg_load(const StFile& st, KxSizes& z) {
 
 // one layer: x += rms(mixer(x)) * w1, then x += rms(ff(x)) * w2
 void b200rwkv_engine::dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int nslot_grid, bool decode, int nsplit, Profiler* prof) {
-    Kemirax& m = *kx;
+    SeqModel& m = *kx;
     const int W = m.W;
     MetaView mv{d_meta, maxT, S};
     const int* cntT = d_meta;

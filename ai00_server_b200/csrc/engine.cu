@@ -515,8 +515,9 @@ struct b200rwkv_engine {
 
     std::mutex mu, sm_mu;
 
-    // Kemirax family (kemirax.cuh): set instead of `layers` when the model comes with a config.json of that architecture
-    std::unique_ptr<Kemirax> kx;
+    // families that come with a config.json (Kemirax: kemirax.cuh, Degavik: degavik.cuh): set instead of `layers`; one model object,
+    // step function, page pool and slot memory for all of them
+    std::unique_ptr<SeqModel> kx;
     int kv_tokens = 0, kv_page = 0;               // attention cache capacity (tokens over all live sequences) and page size
     void kx_build(const StFile& st, const char* cfg_json, size_t cfg_len);
     void kx_load(const StFile& st, KxSizes& z);
@@ -2191,7 +2192,7 @@ static void snapshot_copy(b200rwkv_engine* e, int slot, float* buf, bool to_snap
 static Snapshot snapshot_alloc(b200rwkv_engine* e, bool with_logits, int pos = 0) {
     Snapshot sn;
     const size_t rec = 2 * (size_t)e->C + (size_t)e->Hl * e->N * e->N;
-    sn.bytes = e->kx ? e->kx->flat_floats(pos) * 4 : rec * e->L * 4;      // Kemirax: a compact record with `pos` cache rows per layer
+    sn.bytes = e->kx ? e->kx->flat_floats(pos) * 4 : rec * e->L * 4;      // config.json families: a compact record with `pos` cache rows per layer
     sn.pos = pos;
     CK(cudaMalloc(&sn.buf, sn.bytes));
     if (with_logits) {
@@ -2760,7 +2761,7 @@ int32_t b200rwkv_debug_read(b200rwkv_engine* e, const char* name, float* out, si
         if (e->kx) {
             // "layers_on": keep the residual stream after every layer of the following steps (un-graphed); "layers": read it,
             // [num_layer][128 token rows][num_emb]
-            Kemirax& m = *e->kx;
+            SeqModel& m = *e->kx;
             if (n == "layers_on") {
                 if (!m.dbg_layers) m.dbg_layers = (float*)e->dalloc((size_t)e->L * e->maxT * m.W * 4);
                 e->use_graph = false;

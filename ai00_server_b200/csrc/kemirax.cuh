@@ -263,7 +263,8 @@ struct KxSizes {
     int max_top = 1, max_E = 1;
 };
 
-struct Kemirax {
+// the device-side model of every config.json family (which one: cfg.family) and the sequence memory of its slots
+struct SeqModel {
     KxConfig cfg;
     std::vector<KxLayer> layers;
     bool exact = false;

@@ -58,7 +58,7 @@ float* b200rwkv_engine::kx_up32(const std::vector<float>& v) {
     return d;
 }
 
-size_t Kemirax::flat_floats(int ctx_rows) const {
+size_t SeqModel::flat_floats(int ctx_rows) const {
     size_t n = 4;                                          // [0] tokens held
     for (const KxLayer& l : layers) {
         for (const KxLayer::Block& b : l.fixed) n += b.per_slot;
@@ -69,7 +69,7 @@ size_t Kemirax::flat_floats(int ctx_rows) const {
 
 // tensors of a Kemirax model -> device, stacked / interleaved / transposed as the grouped launches want them
 void b200rwkv_engine::kx_load(const StFile& st, KxSizes& z) {
-    Kemirax& m = *kx;
+    SeqModel& m = *kx;
     const int W = m.W, nl = (int)m.cfg.layers.size();
     m.embed = kx_up16(kx_host_bf16(st, "embed", m.V, W));
     m.head = kx_up16(kx_host_bf16(st, "head", m.V, W));
@@ -185,8 +185,8 @@ void b200rwkv_engine::kx_load(const StFile& st, KxSizes& z) {
 }
 
 void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cfg_len) {
-    kx.reset(new Kemirax());
-    Kemirax& m = *kx;
+    kx.reset(new SeqModel());
+    SeqModel& m = *kx;
     m.cfg = kx_parse_config(cfg_json, cfg_len);
     m.exact = precision == 1;
     m.W = m.cfg.width; m.V = m.cfg.vocab;
@@ -303,7 +303,7 @@ void b200rwkv_engine::kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int ro
 
 void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool decode, int nsplit, Profiler* prof) {
     launches_last_step = 0;
-    Kemirax& m = *kx;
+    SeqModel& m = *kx;
     const int W = m.W;
     MetaView mv{d_meta, maxT, S};
     const int* cntT = d_meta;            // T
@@ -432,7 +432,7 @@ static inline int kx_bucket(int n) {
 
 // positions, attention chunks and page-table updates of one step; hands out pages
 void b200rwkv_engine::kx_fill_step(int* hm, const std::vector<int>& slots, const std::vector<int>& counts, bool* decode, int* nsplit) {
-    Kemirax& m = *kx;
+    SeqModel& m = *kx;
     int* base = hm + MetaView::ints(maxT, S);
     int* tok_pos = base + 8;
     int* ch_start = base + 8 + maxT;
@@ -525,7 +525,7 @@ void b200rwkv_engine::kx_run_step(int T, int R, bool decode, int nsplit) {
 
 // ---- sequence memory <-> flat record: [4 header floats][per layer: its fixed blocks (shift row, recurrent state, ...) | cache rows x D] ----
 void b200rwkv_engine::kx_release(int slot) {
-    Kemirax& m = *kx;
+    SeqModel& m = *kx;
     for (int pg : m.pages[slot]) m.free_pages.push_back(pg);
     m.pages[slot].clear();
     m.pos[slot] = 0;
@@ -546,7 +546,7 @@ __global__ void kx_cache_rows_kernel(const KxRowsParams p) {
 
 // export (import = false): slot -> record with `ctx_rows` cache rows per layer; import: record holding `n` tokens -> slot
 void b200rwkv_engine::kx_xfer(int slot, float* rec, int ctx_rows, bool import, int n) {
-    Kemirax& m = *kx;
+    SeqModel& m = *kx;
     if (import) {
         kx_release(slot);
         REQUIRE(n >= 0 && n <= ctx_rows, B200RWKV_ERR_INVALID, "state record holds more tokens than it has rows");
@@ -580,7 +580,7 @@ void b200rwkv_engine::kx_xfer(int slot, float* rec, int ctx_rows, bool import, i
 }
 
 // host copy between two records of the same model whose cache blocks have different row counts
-static void kx_relayout(const Kemirax& m, const float* src, int src_rows, float* dst, int dst_rows, int n) {
+static void kx_relayout(const SeqModel& m, const float* src, int src_rows, float* dst, int dst_rows, int n) {
     size_t a = 4, b = 4;
     memset(dst, 0, 16);                                    // header: the caller writes the token count
     for (const KxLayer& l : m.layers) {
@@ -594,7 +594,7 @@ static void kx_relayout(const Kemirax& m, const float* src, int src_rows, float*
 
 // an empty sequence in `slot`: pages back to the pool, the fixed blocks (shift rows, recurrent states, convolution tails) zero
 void b200rwkv_engine::kx_reset(int slot) {
-    Kemirax& m = *kx;
+    SeqModel& m = *kx;
     kx_release(slot);
     for (KxLayer& l : m.layers)
         for (const KxLayer::Block& b : l.fixed)
