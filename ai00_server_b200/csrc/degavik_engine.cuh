@@ -186,6 +186,18 @@ void b200rwkv_engine::dg_load(const StFile& st, KxSizes& z) {
         }
         m.max_split = std::min(m.max_split, cl);
     }
+    m.wa_ctas_prompt = m.wa_ctas_decode = 8;
+    for (const KxLayer& l : m.layers) {
+        if (l.c.mixer != KX_WINDOW) continue;
+        const int G_ = l.c.kv_heads, H_ = l.c.heads;
+        const int thr_p = std::min(l.wa_gt, G_) * cdiv(qb * (H_ / G_), WA_RB) >= 16 ? WA_THREADS : 256;
+        const int thr_d = std::min(l.wa_gt, G_) * cdiv(H_ / G_, WA_RB) >= 16 ? WA_THREADS : 256;
+        int np = 1, nd = 1;
+        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&np, window_attn_kernel, thr_p, window_attn_smem(qb, H_, l.c.dim, l.c.vdim, l.wa_gt)));
+        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nd, window_attn_kernel, thr_d, window_attn_smem(1, H_, l.c.dim, l.c.vdim, l.wa_gt)));
+        m.wa_ctas_prompt = std::max(1, std::min(m.wa_ctas_prompt, np));
+        m.wa_ctas_decode = std::max(1, std::min(m.wa_ctas_decode, nd));
+    }
     REQUIRE((size_t)W * 4 <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "width too large for the output-norm kernel");
     CK(cudaFuncSetAttribute(norm_add_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
 }
@@ -239,7 +251,7 @@ void b200rwkv_engine::dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int
                             c.softcap, qb, l.wa_gt, nsplit, mv, m.sm};
         launch_cluster = nsplit;
         // 16 warps where the score / value phases have a work item (four rows of one key head) for each, 8 otherwise
-        const int items = std::min(l.wa_gt, G_) * cdiv(qb * (H_ / G_), WA_RB);
+        const int items = std::min(l.wa_gt, G_) * cdiv(qb * (H_ / G_), WA_RB);      // qb = 1 in decode steps
         launch_k(window_attn_kernel, dim3((decode ? rows : cdiv(rows, qb) + nslot_grid) * nsplit), dim3(items >= 16 ? WA_THREADS : 256),
                  window_attn_smem(qb, H_, dk, dv, l.wa_gt), wp, KC_WKV, s, prof);
     }

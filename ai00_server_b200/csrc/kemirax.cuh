@@ -272,6 +272,7 @@ struct SeqModel {
     float final_gain = 1.f;
     float* final_w = nullptr;                     // weight vector of the last norm (families that have one)
     int qb_prompt = 4;                            // tokens per attention chunk of a prompt step
+    int wa_ctas_prompt = 1, wa_ctas_decode = 1;   // windowed-attention CTAs one SM holds at once (prompt / decode shape)
     float *y = nullptr, *cv = nullptr, *gl = nullptr;   // sublayer output, convolution output, output-gate logits
     __nv_bfloat16 *embed = nullptr, *head = nullptr;
     // sequence memory

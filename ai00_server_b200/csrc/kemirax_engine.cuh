@@ -484,7 +484,8 @@ void b200rwkv_engine::kx_fill_step(int* hm, const std::vector<int>& slots, const
             if (l.c.mixer == KX_WINDOW) seen = std::max(seen, std::min(ctx_max, l.c.window + l.c.keep_first + QB));
         const int tiles = cdiv(seen, WA_KT);
         ns = 1;
-        while (ns < m.max_split && std::max(1, nch) * ns < num_sms && tiles / (ns * 2) >= 1) ns *= 2;
+        const int room = num_sms * (dec ? m.wa_ctas_decode : m.wa_ctas_prompt);         // CTAs the GPU holds at once
+        while (ns < m.max_split && std::max(1, nch) * ns * 2 <= room && tiles / (ns * 2) >= 1) ns *= 2;   // at most one wave of CTAs
     }
     *decode = dec; *nsplit = ns;
 }
